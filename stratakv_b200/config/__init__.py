@@ -2,8 +2,9 @@ from .llama import ConfigError, LlamaConfig
 from .registry import (Architecture, known_architectures, load_config, read_config_json,
                        register_architecture, resolve_architecture)
 from .engine import EngineConfig
+from .kedelorn import KedelornConfig
 from .povusun import PovusunConfig
 from .zepavik import ZepavikConfig
 
-__all__ = ["ConfigError", "LlamaConfig", "ZepavikConfig", "PovusunConfig", "EngineConfig", "Architecture", "known_architectures",
+__all__ = ["ConfigError", "LlamaConfig", "ZepavikConfig", "PovusunConfig", "KedelornConfig", "EngineConfig", "Architecture", "known_architectures",
            "load_config", "read_config_json", "register_architecture", "resolve_architecture"]

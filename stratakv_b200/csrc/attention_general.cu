@@ -212,7 +212,8 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                          const int* __restrict__ token_seq, T* __restrict__ out, int n_tokens, int num_heads,
                          int num_kv_heads, int dim, int vdim, int block_size, float scale, int window,
                          const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ gate,
-                         int gate_stride, int out_stride, float softcap, int gate_per_element) {
+                         int gate_stride, int out_stride, float softcap, int gate_per_element,
+                         const float* __restrict__ sink, int v_stride) {
     extern __shared__ __align__(16) float general_q[];          // [GEN_WARPS][dim rounded up to 4]
     pdl_launch_dependents();
     pdl_wait();
@@ -259,7 +260,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         for (int jj = 0; jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, jj);
-            const T* v_row = v_cache + (size_t)rj * vdim;
+            const T* v_row = v_cache + (size_t)rj * v_stride;
 #pragma unroll
             for (int i = 0; i < GEN_ACC; ++i) {
                 const int d = lane + 32 * i;
@@ -267,6 +268,8 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
             }
         }
     }
+    // a sink counts once in the denominator: it has no key and no value, and is not scaled
+    if (sink) running_sum += expf(sink[head] - running_max);
     float factor = 1.0f / running_sum;
     if (gate && !gate_per_element) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + head]));
     const float* gate_row = gate && gate_per_element ? gate + (size_t)t * gate_stride + (size_t)head * vdim : nullptr;
@@ -331,18 +334,21 @@ SKV_EXPORT int skv_paged_gather(const void* cache, const int* block_table, int t
 
 // `r1`, `r2`: float [num_heads] or both null.  `gate`: float, the gate's logit of (token t, head h) at
 // gate[t * gate_stride + h], or null.  `out` rows are out_stride >= heads * vdim apart; what lies beyond a row's
-// heads is set to zero.
+// heads is set to zero.  `sink`: float [num_heads] or null; exp(sink[h]) is added to the softmax's denominator.
+// `value_stride`: numbers between the values' rows (0: vdim), so that the head of a wider cached row can be the value.
 SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                      int table_width, const int* positions, const int* token_seq, void* out,
                                      int n_tokens, int num_heads, int num_kv_heads, int dim, int vdim, int block_size,
                                      float scale, int window, const float* r1, const float* r2, const float* gate,
                                      int gate_stride, int out_stride, float softcap, int gate_per_element,
-                                     cudaStream_t stream) {
+                                     const float* sink, int value_stride, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_general", "heads must be a positive multiple of kv heads");
     if (dim <= 0 || vdim <= 0 || vdim > GEN_MAX_VDIM) return fail("skv_attention_general", "value heads of 1 to 512 numbers are served");
     if (softcap < 0.0f) return fail("skv_attention_general", "the cap on the scores must not be negative");
+    if (value_stride <= 0) value_stride = vdim;
+    if (value_stride < vdim) return fail("skv_attention_general", "the values' rows cannot be closer together than they are wide");
     if (block_size <= 0 || window < 0) return fail("skv_attention_general", "bad block size or window");
     if (out_stride < num_heads * vdim) return fail("skv_attention_general", "a row of the output is shorter than its heads");
     if ((r1 == nullptr) != (r2 == nullptr)) return fail("skv_attention_general", "the distance bias needs both of its numbers per head");
@@ -356,5 +362,5 @@ SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const v
                       dim3(GEN_WARPS * 32), smem, stream, (const skv_t*)q, (const skv_t*)k_cache,
                       (const skv_t*)v_cache, block_table, table_width, positions, token_seq, (skv_t*)out, n_tokens,
                       num_heads, num_kv_heads, dim, vdim, block_size, scale, window, r1, r2, gate, gate_stride, out_stride,
-                      softcap, gate_per_element);
+                      softcap, gate_per_element, sink, value_stride);
 }

@@ -15,7 +15,7 @@ constexpr int HW_TOKENS = 32, HW_OUTS = 64, HW_K = 32;
 template <typename TIn, typename TOut, typename TW>
 __global__ void __launch_bounds__(256)
 headwise_linear_kernel(const TIn* __restrict__ x, int x_stride, const TW* __restrict__ w, TOut* __restrict__ out,
-                       int out_stride, int n_tokens, int in_dim, int out_dim, int zero_pad) {
+                       int out_stride, int n_tokens, int in_dim, int out_dim, int zero_pad, int out_head_stride) {
     __shared__ float xs[HW_TOKENS][HW_K + 1];
     __shared__ float ws[HW_OUTS][HW_K + 1];
     pdl_launch_dependents();
@@ -56,7 +56,7 @@ headwise_linear_kernel(const TIn* __restrict__ x, int x_stride, const TW* __rest
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int o = o0 + tx + 16 * j;
-            if (o < out_dim) out[(size_t)t * out_stride + (size_t)head * out_dim + o] = from_float<TOut>(acc[i][j]);
+            if (o < out_dim) out[(size_t)t * out_stride + (size_t)head * out_head_stride + o] = from_float<TOut>(acc[i][j]);
         }
     }
     // columns that pad a row for the projection after it are zero
@@ -71,32 +71,37 @@ headwise_linear_kernel(const TIn* __restrict__ x, int x_stride, const TW* __rest
 
 template <typename TIn, typename TOut>
 static int launch_headwise(const void* x, int x_stride, const void* w, void* out, int out_stride, int n_tokens,
-                           int heads, int in_dim, int out_dim, int zero_pad, cudaStream_t stream) {
+                           int heads, int in_dim, int out_dim, int zero_pad, int out_head_stride, cudaStream_t stream) {
     const dim3 grid((out_dim + HW_OUTS - 1) / HW_OUTS, (n_tokens + HW_TOKENS - 1) / HW_TOKENS, heads);
     return launch_pdl("skv_headwise_linear", headwise_linear_kernel<TIn, TOut, skv_t>, grid, dim3(256), 0, stream,
-                      (const TIn*)x, x_stride, (const skv_t*)w, (TOut*)out, out_stride, n_tokens, in_dim, out_dim, zero_pad);
+                      (const TIn*)x, x_stride, (const skv_t*)w, (TOut*)out, out_stride, n_tokens, in_dim, out_dim, zero_pad,
+                      out_head_stride);
 }
 
 }  // namespace skv
 
 using namespace skv;
 
+// out_head_stride: head h of an out row starts at h * out_head_stride (0: out_dim, the heads side by side).
 // x_is_float / out_is_float: 1 for float, 0 for the compute dtype.  zero_pad: the columns of an out row beyond its
 // heads are set to zero.
 SKV_EXPORT int skv_headwise_linear(const void* x, int x_is_float, int x_stride, const void* w, void* out,
                                    int out_is_float, int out_stride, int n_tokens, int heads, int in_dim, int out_dim,
-                                   int zero_pad, cudaStream_t stream) {
+                                   int zero_pad, int out_head_stride, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || in_dim <= 0 || out_dim <= 0) return fail("skv_headwise_linear", "sizes must be positive");
     if (heads > 65535 || (n_tokens + HW_TOKENS - 1) / HW_TOKENS > 65535)
         return fail("skv_headwise_linear", "too many heads or tokens for one launch");
-    if (x_stride < heads * in_dim || out_stride < heads * out_dim)
+    if (out_head_stride <= 0) out_head_stride = out_dim;
+    if (x_stride < heads * in_dim || out_head_stride < out_dim || out_stride < (heads - 1) * out_head_stride + out_dim)
         return fail("skv_headwise_linear", "a row is shorter than its heads");
+    if (zero_pad && out_head_stride != out_dim)
+        return fail("skv_headwise_linear", "zero_pad goes with heads that lie side by side");
     if (x_is_float && out_is_float)
-        return launch_headwise<float, float>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, stream);
+        return launch_headwise<float, float>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, out_head_stride, stream);
     if (x_is_float)
-        return launch_headwise<float, skv_t>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, stream);
+        return launch_headwise<float, skv_t>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, out_head_stride, stream);
     if (out_is_float)
-        return launch_headwise<skv_t, float>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, stream);
-    return launch_headwise<skv_t, skv_t>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, stream);
+        return launch_headwise<skv_t, float>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, out_head_stride, stream);
+    return launch_headwise<skv_t, skv_t>(x, x_stride, w, out, out_stride, n_tokens, heads, in_dim, out_dim, zero_pad, out_head_stride, stream);
 }

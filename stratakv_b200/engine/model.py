@@ -148,6 +148,8 @@ class Model:
             step.norm_after_layer = readers[index + 1]
             following = spec.schedule[index + 1].layer if index + 1 < len(spec.schedule) else None
             step.next_layer_norm = self.layers[following].mixer_norm if following is not None else None
+            step.next_layer = self.layers[following] if following is not None else None
+            step.run_index = index
             self.layers[entry.layer].forward(step, x, entry)
             if self.layer_probe is not None:
                 self.layer_probe(index, x)

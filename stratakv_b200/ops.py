@@ -24,6 +24,9 @@ ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "r
 # activations that take one number (``activation_param``): the clamp of both branches of "swiglu_clamp", a gated unit
 # min(g, c) * sigmoid(1.702 min(g, c)) * (clamp(u, -c, c) + 1); it is an activation of gated projections only
 PARAMETRIC_ACTIVATIONS = ("swiglu_clamp",)
+# what the kernels of a routed feed-forward are built for (csrc/routed_mlp.cu)
+MAX_EXPERTS, MAX_EXPERTS_PER_TOKEN = 1024, 16
+MAX_STREAMS = 8            # copies of the residual stream that ``stream_mix`` takes (csrc/stream_mix.cu)
 
 
 def activation_word(activation: str, param: float = 0.0):
@@ -522,8 +525,11 @@ class Kernels:
     def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads: int,
                           num_kv_heads: int, dim: int, vdim: int, block_size: int, scale: float, window: int = 0,
                           r1=None, r2=None, gate=None, gate_stride: int = 0, softcap: float = 0.0,
-                          gate_per_element: bool = False):
-        """(``softcap`` c > 0: scores become ``c * tanh(score / c)``.  ``gate_per_element``: the gate holds a logit for
+                          gate_per_element: bool = False, sink=None, value_stride: int = 0):
+        """(``sink``, float32 per head: ``exp(sink[h])`` counts once in the softmax's denominator, with no value.
+        ``value_stride``: the values' rows are that many numbers apart where they are not ``vdim`` wide, so that the
+        first ``vdim`` numbers of the cached keys can serve as the values.)
+        (``softcap`` c > 0: scores become ``c * tanh(score / c)``.  ``gate_per_element``: the gate holds a logit for
         every output number, token t, head h, number d at ``[t * gate_stride + h * vdim + d]``.)
         Attention with run-time head sizes (keys ``dim``, values ``vdim``), a warp per (token, head), float math.
         ``r1``, ``r2`` (float32 per head): ``r1 * ln(1 + r2 * distance)`` is taken off each score.  ``gate``
@@ -533,12 +539,19 @@ class Kernels:
         self._want(k_cache, self.dtype, "k_cache"); self._want(v_cache, self.dtype, "v_cache")
         self._want(block_table, torch.int32, "block_table")
         self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        value_stride = value_stride or vdim
+        if value_stride < vdim:
+            raise KernelError("attention_general: the values' rows cannot be closer together than they are wide")
+        if sink is not None:
+            self._want(sink, torch.float32, "sink")
+            if sink.numel() != num_heads:
+                raise KernelError("attention_general: the sink must hold one number per head")
         for name, value in (("r1", r1), ("r2", r2)):
             if value is not None:
                 self._want(value, torch.float32, name)
                 if value.numel() != num_heads:
                     raise KernelError(f"attention_general: {name} must hold one number per head")
-        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda
+        if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda or gate.stride(-1) != 1
                                  or gate_stride < num_heads * (vdim if gate_per_element else 1)):
             raise KernelError("attention_general: the gate must be float32 on the GPU, a row at least heads wide")
         n = q.shape[0]
@@ -548,7 +561,7 @@ class Kernels:
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
             _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, dim, vdim, block_size, ctypes.c_float(scale),
             window, _ptr(r1), _ptr(r2), _ptr(gate), gate_stride, out.shape[1], ctypes.c_float(softcap),
-            int(bool(gate_per_element)), _stream()), "attention_general")
+            int(bool(gate_per_element)), _ptr(sink), int(value_stride), _stream()), "attention_general")
 
     def paged_gather(self, cache, block_table, positions, seqs, out):
         """``out[i, :]`` = the row that a one-head paged cache (``[blocks, 1, block_size, width]``) holds for position
@@ -603,10 +616,11 @@ class Kernels:
             _ptr(proj_t), _ptr(norm_w), ctypes.c_float(eps), _ptr(next_gamma), ctypes.c_float(next_eps), _ptr(next_out),
             n, hidden, _ptr(branch), _ptr(post_gamma), ctypes.c_float(post_eps), _stream()), "token_side")
 
-    def headwise_linear(self, x, w, out, heads: int, zero_pad: bool = False):
+    def headwise_linear(self, x, w, out, heads: int, zero_pad: bool = False, out_head_stride: int = 0):
         """``out[t, h, :] = w[h] . x[t, h, :]`` with ``w`` ``[heads, out_dim, in_dim]`` in the compute dtype; ``x`` and
         ``out`` are 2-D, float32 or the compute dtype, head h at columns ``h * in_dim`` and ``h * out_dim`` (rows may be
-        wider; ``zero_pad`` sets what lies beyond an out row's heads to zero).  Sums are float32."""
+        wider; ``zero_pad`` sets what lies beyond an out row's heads to zero).  Sums are float32.  ``out_head_stride``: head h
+        of ``out`` starts at ``h * out_head_stride`` instead (what lies between the heads' results is left alone)."""
         self._want(w, self.dtype, "w")
         for name, tensor in (("x", x), ("out", out)):
             if not tensor.is_cuda or tensor.dtype not in (torch.float32, self.dtype) or tensor.dim() != 2 \
@@ -616,11 +630,16 @@ class Kernels:
             raise KernelError("headwise_linear: the weight must be [heads, out_dim, in_dim]")
         out_dim, in_dim = w.shape[1], w.shape[2]
         n = x.shape[0]
-        if out.shape[0] != n or x.shape[1] < heads * in_dim or out.shape[1] < heads * out_dim:
+        out_head_stride = out_head_stride or out_dim
+        if (out.shape[0] != n or x.shape[1] < heads * in_dim or out_head_stride < out_dim
+                or out.shape[1] < (heads - 1) * out_head_stride + out_dim):
             raise KernelError("headwise_linear: a row is shorter than its heads")
+        if zero_pad and out_head_stride != out_dim:
+            raise KernelError("headwise_linear: zero_pad goes with heads that lie side by side")
         self._check(self.lib.skv_headwise_linear(
             _ptr(x), int(x.dtype == torch.float32), x.stride(0), _ptr(w), _ptr(out), int(out.dtype == torch.float32),
-            out.stride(0), n, heads, in_dim, out_dim, int(bool(zero_pad)), _stream()), "headwise_linear")
+            out.stride(0), n, heads, in_dim, out_dim, int(bool(zero_pad)), int(out_head_stride), _stream()),
+            "headwise_linear")
 
     def _recurrent_batch(self, step_meta, state, channels: int, taps: int, name: str):
         positions, token_seq, cu_q, slot_ids = step_meta
@@ -697,6 +716,201 @@ class Kernels:
             *self._recurrent_batch(step_meta, state, channels, taps, "rglru_scan"), _stream()), "rglru_scan")
         if summary is not None and self.rglru_scan_scratch(n_seqs, max_q_len, channels) > 0:
             Kernels.launches += 1              # (the pass that sums up the chunks)
+
+    # ---- several copies of the residual stream ---------------------------------------
+    def stream_mix(self, streams, count: int, source=None, branch=None, mix=None, write=None, read=None, gamma=None,
+                   eps: float = 0.0, normed_out=None, sum_out=None):
+        """One pass over ``count`` copies of the residual stream (float32 ``[count, tokens, hidden]``).  The old
+        streams are ``streams``, or all equal to ``source`` (float32 ``[tokens, hidden]``) where they have not been
+        written yet.  With ``branch`` (a sublayer's result), ``mix`` ``[from * count + to]`` and ``write``: every stream
+        becomes ``sum_s mix[s, t] x_s + write[t] * branch`` and is written.  With ``read``, ``gamma`` and ``normed_out``
+        (compute dtype): ``u = sum_t read[t] x_t`` of the (new) streams, ``normed_out = u / sqrt(mean(u^2) + eps) * gamma``.
+        With ``sum_out``: the sum of the (new) streams."""
+        self._want(streams, torch.float32, "streams")
+        if streams.dim() != 3 or streams.shape[0] != count or not 1 <= count <= MAX_STREAMS:
+            raise KernelError(f"stream_mix: the streams must be [count, tokens, hidden] with 1 to {MAX_STREAMS} copies")
+        n, hidden = streams.shape[1], streams.shape[2]
+        for name, tensor in (("source", source), ("branch", branch), ("sum_out", sum_out)):
+            if tensor is not None:
+                self._want(tensor, torch.float32, name)
+                if tuple(tensor.shape) != (n, hidden):
+                    raise KernelError(f"stream_mix: {name} must be [tokens, hidden]")
+        if (branch is None) != (mix is None) or (branch is None) != (write is None):
+            raise KernelError("stream_mix: an update needs the sublayer's result, the mixing matrix and the write weights")
+        if branch is None and source is not None and normed_out is None and sum_out is None:
+            raise KernelError("stream_mix: nothing to do")
+        for name, tensor, size in (("mix", mix, count * count), ("write", write, count), ("read", read, count),
+                                   ("gamma", gamma, hidden)):
+            if tensor is not None:
+                self._want(tensor, torch.float32, name)
+                if tensor.numel() != size:
+                    raise KernelError(f"stream_mix: {name} must hold {size} numbers")
+        if (normed_out is None) != (read is None) or (normed_out is None) != (gamma is None):
+            raise KernelError("stream_mix: a reading needs the read weights, the norm's weight and a place for the result")
+        if normed_out is not None:
+            self._want(normed_out, self.dtype, "normed_out")
+            if tuple(normed_out.shape) != (n, hidden):
+                raise KernelError("stream_mix: normed_out must be [tokens, hidden]")
+        self._check(self.lib.skv_stream_mix(
+            _ptr(streams), int(count), _ptr(source), _ptr(branch), _ptr(mix), _ptr(write), _ptr(read), _ptr(gamma),
+            ctypes.c_float(eps), _ptr(normed_out), _ptr(sum_out), n, hidden, _stream()), "stream_mix")
+
+    # ---- retention ----------------------------------------------------------------------
+    def retention_scratch(self, n_seqs: int, max_q_len: int, heads: int, dim: int, vdim: int) -> int:
+        """Floats of scratch ``retention`` needs for a step whose longest sequence brings ``max_q_len`` tokens."""
+        self.lib.skv_retention_scratch.restype = ctypes.c_longlong
+        return int(self.lib.skv_retention_scratch(int(n_seqs), int(max_q_len), int(heads), int(dim), int(vdim)))
+
+    def retention(self, fused, cos_sin, rotated: int, decay, eps: float, out, state, step_meta, heads: int, dim: int,
+                  vdim: int, max_q_len: int, scratch=None):
+        """Retention over a packed step.  ``fused`` (float32 rows ``[q | k | v | gate]``: ``heads * dim`` twice, then
+        ``heads * vdim`` twice; queries and keys are rotated in place): per head ``S <- decay S + k v^T`` with
+        ``k = rot(k) * dim^-1/2`` from and to ``state`` (float32 ``[slots, 2 * heads * dim * vdim]``: S in the half of
+        the last written position's parity), ``o = S^T rot(q)``, ``out = o / rms(o) * silu(gate)`` per head in the
+        compute dtype (columns beyond the heads are set to zero).  ``cos_sin``: ``[positions, rotated / 2, 2]`` or None.
+        ``step_meta``: the step's ``(positions, token_seq, cu_q, slot_ids)``; ``scratch``: ``retention_scratch`` floats."""
+        self._want(fused, torch.float32, "fused"); self._want(decay, torch.float32, "decay")
+        self._want(out, self.dtype, "out"); self._want(state, torch.float32, "state")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        for label, tensor in (("positions", positions), ("token_seq", token_seq), ("cu_q", cu_q), ("slot_ids", slot_ids)):
+            self._want(tensor, torch.int32, label)
+        n, n_seqs = fused.shape[0], slot_ids.numel()
+        if (fused.shape[1] < 2 * heads * (dim + vdim) or out.shape[0] != n or out.shape[1] < heads * vdim
+                or decay.numel() != heads or positions.numel() != n or cu_q.numel() != n_seqs + 1):
+            raise KernelError("retention: shapes do not agree")
+        if state.dim() != 2 or state.shape[1] < 2 * heads * dim * vdim:
+            raise KernelError("retention: the state must be [slots, 2 * heads * dim * vdim or wider] float32")
+        if cos_sin is not None:
+            self._want(cos_sin, torch.float32, "cos_sin")
+            if rotated <= 0 or rotated % 2 or rotated > dim or tuple(cos_sin.shape[1:]) != (rotated // 2, 2):
+                raise KernelError("retention: the rotation's table must be [positions, rotated / 2, 2]")
+        need = self.retention_scratch(n_seqs, max_q_len, heads, dim, vdim)
+        if need:
+            self._want(scratch, torch.float32, "scratch")
+            if scratch.numel() < need:
+                raise KernelError("retention: the scratch for the chunks is too small")
+        self._check(self.lib.skv_retention(
+            _ptr(fused), fused.shape[1], _ptr(cos_sin), int(rotated if cos_sin is not None else 0),
+            cos_sin.shape[0] if cos_sin is not None else 0, _ptr(decay), ctypes.c_float(eps), _ptr(out), out.shape[1],
+            _ptr(scratch), n, n_seqs, heads, dim, vdim, int(max_q_len), _ptr(positions), _ptr(token_seq), _ptr(cu_q),
+            _ptr(slot_ids), _ptr(state), state.shape[1], _stream()), "retention")
+
+    # ---- latent attention with a rotated part ---------------------------------------------
+    def latent_finish(self, fused, q_plain, q_folded, cache, positions, token_seq, block_table, heads: int, dim: int,
+                      rope_dim: int, latent_dim: int, block_size: int, rotation=None, rotated: int = 0,
+                      latent_offset: int = 0, latent_gamma=None, eps: float = 0.0, write_cache: bool = True):
+        """From float32 rows of a fused projection ``[queries: heads x (dim | rope_dim) | latent_dim + rope_dim | ...]``:
+        the unrotated query parts to ``q_plain`` ``[tokens, heads * dim]``, the rotated ones (first ``rotated`` numbers
+        turned by ``rotation`` ``[positions, rotated / 2, 2]``) to the last ``rope_dim`` columns of every head of
+        ``q_folded`` ``[tokens, heads * (latent_dim + rope_dim)]``; with ``write_cache`` the latent, divided by its root
+        mean square and times ``latent_gamma``, and the rotated key part behind it go to the token's row of ``cache``
+        ``[blocks, 1, block_size, latent_dim + rope_dim]``."""
+        self._want(fused, torch.float32, "fused"); self._want(q_plain, self.dtype, "q_plain")
+        self._want(q_folded, self.dtype, "q_folded"); self._want(cache, self.dtype, "cache")
+        self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
+        self._want(block_table, torch.int32, "block_table")
+        n, key_dim = fused.shape[0], latent_dim + rope_dim
+        if (tuple(q_plain.shape) != (n, heads * dim) or tuple(q_folded.shape) != (n, heads * key_dim)
+                or tuple(cache.shape[1:]) != (1, block_size, key_dim) or positions.numel() != n or token_seq.numel() != n):
+            raise KernelError("latent_finish: shapes do not agree")
+        if fused.shape[1] < heads * (dim + rope_dim) + (key_dim if write_cache else 0) or (write_cache and latent_offset < heads * (dim + rope_dim)):
+            raise KernelError("latent_finish: a row is shorter than its queries, latent and key part")
+        if rotation is not None:
+            self._want(rotation, torch.float32, "rotation")
+            if rotated <= 0 or rotated % 2 or rotated > rope_dim or tuple(rotation.shape[1:]) != (rotated // 2, 2):
+                raise KernelError("latent_finish: the rotation's table must be [positions, rotated / 2, 2]")
+        if write_cache:
+            self._want(latent_gamma, torch.float32, "latent_gamma")
+            if latent_gamma.numel() != latent_dim:
+                raise KernelError("latent_finish: the latent's norm weight must hold latent_dim numbers")
+        self._check(self.lib.skv_latent_finish(
+            _ptr(fused), fused.shape[1], _ptr(q_plain), _ptr(q_folded), _ptr(cache), _ptr(positions), _ptr(token_seq),
+            _ptr(block_table), block_table.shape[1], n, heads, dim, rope_dim, latent_dim, block_size, _ptr(rotation),
+            int(rotated if rotation is not None else 0), rotation.shape[0] if rotation is not None else 0,
+            int(latent_offset), _ptr(latent_gamma), ctypes.c_float(eps), int(bool(write_cache)), _stream()), "latent_finish")
+
+    # ---- routed feed-forward ------------------------------------------------------------------
+    def route_tokens(self, h, router_w, correction, top: int, scale: float, renormalize: bool, chosen, weights,
+                     shared_gate_weight=None, shared_gate_out=None):
+        """Per token: ``s = sigmoid(router_w . h)`` (float32 sums); the ``top`` experts with the largest
+        ``s + correction`` (the lower index among equals) into ``chosen`` (int32 ``[tokens, top]``), their ``s * scale``
+        into ``weights`` (``renormalize``: divided by the chosen scores' sum first).  With ``shared_gate_weight``
+        ``[hidden]``: ``shared_gate_out[t] = sigmoid(shared_gate_weight . h[t])``."""
+        self._want(h, self.dtype, "h"); self._want(router_w, self.dtype, "router_w")
+        self._want(chosen, torch.int32, "chosen"); self._want(weights, torch.float32, "weights")
+        n, hidden = h.shape
+        experts = router_w.shape[0]
+        if (router_w.shape[1] != hidden or tuple(chosen.shape) != (n, top) or tuple(weights.shape) != (n, top)
+                or not 0 < top <= min(experts, MAX_EXPERTS_PER_TOKEN) or experts > MAX_EXPERTS):
+            raise KernelError("route_tokens: shapes do not agree")
+        if correction is not None:
+            self._want(correction, torch.float32, "correction")
+            if correction.numel() != experts:
+                raise KernelError("route_tokens: one correction per expert is needed")
+        if (shared_gate_weight is None) != (shared_gate_out is None):
+            raise KernelError("route_tokens: the shared expert's gate needs its weight and a place for the result")
+        if shared_gate_weight is not None:
+            self._want(shared_gate_weight, self.dtype, "shared_gate_weight"); self._want(shared_gate_out, torch.float32, "shared_gate_out")
+            if shared_gate_weight.numel() != hidden or shared_gate_out.numel() != n:
+                raise KernelError("route_tokens: the shared expert's gate has the wrong size")
+        self._check(self.lib.skv_route_tokens(
+            _ptr(h), _ptr(router_w), _ptr(correction), _ptr(shared_gate_weight), n, hidden, experts, int(top),
+            ctypes.c_float(scale), int(bool(renormalize)), _ptr(chosen), _ptr(weights), _ptr(shared_gate_out), _stream()),
+            "route_tokens")
+
+    def sort_by_expert(self, chosen, experts: int, offsets, order, place):
+        """A counting sort of the (token, choice) pairs by expert: ``offsets`` (int32 ``[experts + 1]``) bounds each
+        expert's pairs in the sorted order, ``order[p]`` is the token of sorted pair p, ``place[t, k]`` where pair
+        (t, k) went."""
+        for name, tensor in (("chosen", chosen), ("offsets", offsets), ("order", order), ("place", place)):
+            self._want(tensor, torch.int32, name)
+        n, top = chosen.shape
+        if offsets.numel() != experts + 1 or order.numel() != n * top or tuple(place.shape) != (n, top) or experts > MAX_EXPERTS:
+            raise KernelError("sort_by_expert: shapes do not agree")
+        self._check(self.lib.skv_sort_by_expert(_ptr(chosen), n * top, int(top), int(experts), _ptr(offsets), _ptr(order),
+                                                _ptr(place), _stream()), "sort_by_expert")
+
+    def expert_linear(self, a, w, offsets, out, rows=None, activation: Optional[str] = None):
+        """``out[p] = act(w[e] . a[row(p)])`` for every sorted pair p of expert e (``offsets`` from ``sort_by_expert``);
+        ``w`` ``[experts, N, K]``; ``row(p) = rows[p]`` (the first projection gathers its input from the tokens) or p.
+        ``out`` ``[pairs, N]`` is the compute dtype (with ``activation``) or float32.  Sums are float32."""
+        self._want(a, self.dtype, "a"); self._want(w, self.dtype, "w"); self._want(offsets, torch.int32, "offsets")
+        if out.dtype not in (self.dtype, torch.float32) or not out.is_cuda or not out.is_contiguous():
+            raise KernelError("expert_linear: out must be a contiguous CUDA tensor, float32 or the compute dtype")
+        pairs = out.shape[0]
+        experts, N, K = w.shape
+        if a.shape[1] != K or out.shape[1] != N or offsets.numel() != experts + 1 or (rows is None and a.shape[0] != pairs):
+            raise KernelError("expert_linear: shapes do not agree")
+        if rows is not None:
+            self._want(rows, torch.int32, "rows")
+            if rows.numel() != pairs:
+                raise KernelError("expert_linear: one row index per pair is needed")
+        if activation is not None and (activation not in ACTIVATIONS or activation in PARAMETRIC_ACTIVATIONS):
+            raise KernelError(f"expert_linear: activation '{activation}' is not supported")
+        self._check(self.lib.skv_expert_linear(
+            _ptr(a), a.stride(0), a.shape[0], _ptr(rows), _ptr(w), _ptr(offsets), _ptr(out),
+            int(out.dtype == torch.float32), pairs, experts, N, K, ACTIVATIONS[activation] if activation is not None else -1,
+            _stream()), "expert_linear")
+
+    def combine_experts(self, results, place, weights, shared, share, x, add: bool = True):
+        """``x[t] (+)= sum_k weights[t, k] * results[place[t, k]] + share[t] * shared[t]`` (float32; ``shared`` may be
+        None, ``share`` None counts as one); ``add`` false stores instead of adding."""
+        self._want(results, torch.float32, "results"); self._want(place, torch.int32, "place")
+        self._want(weights, torch.float32, "weights"); self._want(x, torch.float32, "x")
+        n, hidden = x.shape
+        top = place.shape[1]
+        if results.shape[1] != hidden or results.shape[0] != n * top or tuple(weights.shape) != (n, top) or place.shape[0] != n:
+            raise KernelError("combine_experts: shapes do not agree")
+        if shared is not None:
+            self._want(shared, torch.float32, "shared")
+            if tuple(shared.shape) != (n, hidden):
+                raise KernelError("combine_experts: the shared expert's result must be [tokens, hidden]")
+        if share is not None:
+            self._want(share, torch.float32, "share")
+            if shared is None or share.numel() != n:
+                raise KernelError("combine_experts: one gate per token of the shared expert's result is needed")
+        self._check(self.lib.skv_combine_experts(_ptr(results), _ptr(place), _ptr(weights), _ptr(shared), _ptr(share),
+                                                 _ptr(x), n, hidden, top, int(bool(add)), _stream()), "combine_experts")
 
     def scale_inplace(self, x, factor: float):
         self._want(x, torch.float32, "x")

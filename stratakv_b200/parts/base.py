@@ -23,7 +23,7 @@ import torch
 class TensorRequest:
     """A checkpoint tensor a part needs.  ``init`` tells the random-weights mode
     how to fill it: ``normal`` is N(0, std), ``around_one`` is 1 + N(0, std), ``positive`` is
-    0.05 + |N(0, 0.5)|."""
+    0.05 + |N(0, 0.5)|, ``around_identity`` the identity matrix + N(0, std)."""
     shape: Tuple[int, ...]
     init: str = "normal"
 
@@ -122,6 +122,8 @@ class StepBatch:
     residual_stats: Any = None         # residual.ResidualStats when norms may be folded into projections
     norm_after_layer: Any = None       # then: the foldable norm that reads the stream after the running layer
     next_layer_norm: Any = None        # the first norm of the layer that runs next (None after the last)
+    next_layer: Any = None             # the layer that runs next (``block.Layer``; None after the last)
+    run_index: int = 0                 # which entry of the model's schedule is running
     # True while a part is handed a scratch buffer in place of the stream and is to STORE its result there instead
     # of adding it (an arrangement that norms a sublayer's output sets it for parts with ``stores_branch``)
     store_branch: bool = False

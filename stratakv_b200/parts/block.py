@@ -165,6 +165,62 @@ def sandwich(layer: Layer, step, x, entry) -> None:
         stats.invalidate()
 
 
+def multi_stream(layer: Layer, step, x, entry) -> None:
+    """The pre-norm block over several copies of the stream: each sublayer reads a mix of the streams through its
+    norm and its result goes into every stream (``parts/stream_mix.py``).  The streams live in scratch memory
+    ``[streams, tokens, hidden]``; before the first layer they all equal the embedding's output, which ``x`` holds,
+    and after every layer ``x`` is their sum (what the last norm reads).  One kernel brings the streams up to date
+    after a sublayer, reads them for the sublayer after it (this layer's feed-forward, or the next layer's mixer) and
+    applies that one's norm."""
+    link = layer.extra.get("mixer_streams")
+    ffn_link = layer.extra.get("ffn_streams")
+    if layer.mixer_norm is None or layer.mixer is None or link is None:
+        raise ValueError("the multi_stream arrangement needs a norm, a mixer and the mixer's connection to the streams")
+    if layer.ffn is not None and (layer.ffn_norm is None or ffn_link is None):
+        raise ValueError("the multi_stream arrangement needs a norm and a connection for its feed-forward")
+    stats = step.residual_stats
+    if stats is not None:
+        stats.expect(None)                          # nothing here folds a norm into a projection
+    rt = layer.mixer.rt
+    ops = rt.kernels()
+    count = link.spec.streams
+    shape = tuple(x.shape)
+    streams = rt.workspace.get("streams", (count,) + shape, torch.float32)
+    source = x if step.run_index == 0 else None     # the streams have not been written yet: they all equal x
+
+    prepared = step.scratch.pop("normed_ahead", None)
+    if prepared is not None and prepared[0] is layer.mixer_norm:
+        h = prepared[1]
+    else:
+        h = rt.workspace.get("normed", shape, rt.dtype)
+        ops.stream_mix(streams, count, source, read=link.read, gamma=layer.mixer_norm.gamma,
+                       eps=layer.mixer_norm.spec.eps, normed_out=h)
+    branch = _branch(layer.mixer, step, h, shape, entry.cache, entry.writes_cache)
+    if layer.ffn is not None:
+        h = rt.workspace.get("normed", shape, rt.dtype)
+        ops.stream_mix(streams, count, source, branch=branch, mix=link.mix, write=link.write, read=ffn_link.read,
+                       gamma=layer.ffn_norm.gamma, eps=layer.ffn_norm.spec.eps, normed_out=h)
+        source = None
+        branch = _branch(layer.ffn, step, h, shape)
+        link = ffn_link
+    # the layer's last update also leaves the sum of the streams in x and reads them for the next layer
+    following = step.next_layer
+    ahead = ahead_link = None
+    if (following is not None and following.spec.arrangement == "multi_stream" and _fusable(following.mixer_norm)
+            and following.extra["mixer_streams"].spec.streams == count):
+        ahead_link = following.extra["mixer_streams"]
+        ahead = rt.workspace.get("normed_next", shape, rt.dtype)
+    ops.stream_mix(streams, count, source, branch=branch, mix=link.mix, write=link.write,
+                   read=ahead_link.read if ahead is not None else None,
+                   gamma=following.mixer_norm.gamma if ahead is not None else None,
+                   eps=following.mixer_norm.spec.eps if ahead is not None else 0.0, normed_out=ahead, sum_out=x)
+    if ahead is not None:
+        step.scratch["normed_ahead"] = (following.mixer_norm, ahead)
+    if stats is not None:
+        stats.invalidate()
+
+
+register_arrangement("multi_stream", multi_stream)
 register_arrangement("pre_norm", pre_norm)
 register_arrangement("sandwich", sandwich)
 register_arrangement("parallel", parallel)

@@ -7,6 +7,13 @@ keys' up-projection into the queries (``headwise_linear`` with the transposed ma
 the same cached vectors as keys and as values (the attention kernels with one key/value head of ``latent_dim``), and
 applies the values' up-projection to each head's result.  No position encoding.
 
+A design may add (``LatentAttentionSpec``): a rotated part of ``rope_dim`` numbers on every query head and ONE rotated key
+part per position that all heads share, cached behind the latent (the folded query of a head is then
+``[Wuk[h]^T q_plain | q_rotated]`` against the cached ``[c | k_rotated]``, and the values are the first ``latent_dim``
+numbers of the same cached row); a sink per head in the softmax's denominator; a gate per head on the output; and a
+layer that attends over the cache another layer wrote.  Any of these takes the folded way on the general attention
+kernel in both dtypes.
+
 That is how one token a sequence runs, and every step in float32.  A prompt in bfloat16 whose heads have a size the
 tensor-core prompt kernel is built for goes the other way round: the cached vectors of the step's sequences are
 gathered, up-projected by one GEMM into keys and values of all heads, laid out as pages of a scratch cache, and
@@ -21,10 +28,17 @@ from .. import ops as _ops
 from ..cache.kinds import CacheKind, register_cache_kind
 from .attention import _residual_mode, _residual_stats
 from .base import CacheRequest, Mixer, TensorRequest
+from .position import RotaryTable
 from .registry import register_mixer
 
 register_cache_kind(CacheKind("latent", paged=True, windowed=False,
                               block_tensors=lambda request, block_size: {"c": (1, block_size, request.head_dim)}))
+
+
+def _extended(spec) -> bool:
+    """True if the spec uses a mechanism beyond the plain latent: a rotated part, a sink, a gate, a borrowed cache."""
+    return bool(getattr(spec, "rope_dim", 0) or getattr(spec, "sink", None) or getattr(spec, "gate_weight", None)
+                or getattr(spec, "shares_kv", False))
 
 
 class LatentAttention(Mixer):
@@ -38,39 +52,64 @@ class LatentAttention(Mixer):
                              "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
         if spec.latent_dim > 512:
             raise ValueError(f"latent attention: a latent of {spec.latent_dim} numbers is not supported (at most 512)")
-        self.q_dim = spec.num_heads * spec.head_dim
+        self.extended = _extended(spec)
+        self.rope_dim = getattr(spec, "rope_dim", 0)
+        if bool(self.rope_dim) != (getattr(spec, "rope", None) is not None) or (self.rope_dim and spec.rope.dims > self.rope_dim):
+            raise ValueError("latent attention: a rotated part needs its rotation, over at most that many numbers")
+        self.q_head = spec.head_dim + self.rope_dim         # a query head: unrotated numbers, then rotated ones
+        self.key_dim = spec.latent_dim + self.rope_dim      # a cached row: the latent, then the shared rotated key part
+        self.q_dim = spec.num_heads * self.q_head
         self.ctx_dim = spec.num_heads * spec.v_head_dim
         self.ctx_width = -(-self.ctx_dim // 8) * 8          # whole 16 bytes for the output projection
-        self.fused_width = -(-(self.q_dim + spec.latent_dim) // 8) * 8
+        # rows of the fused projection: queries, then (a layer with a cache of its own) the latent and the key part,
+        # then the gate's logits
+        self.shares_kv = bool(getattr(spec, "shares_kv", False))
+        self.gate_offset = self.q_dim + (0 if self.shares_kv else self.key_dim)
+        self.has_gate = getattr(spec, "gate_weight", None) is not None
+        self.fused_width = -(-(self.gate_offset + (spec.num_heads if self.has_gate else 0)) // 8) * 8
+        self.position = RotaryTable(spec.rope, runtime) if self.rope_dim else None
 
     @classmethod
     def expected_tensors(cls, spec):
-        return {spec.q_weight: TensorRequest((spec.num_heads * spec.head_dim, spec.hidden_size)),
-                spec.down_weight: TensorRequest((spec.latent_dim, spec.hidden_size)),
-                spec.latent_norm: TensorRequest((spec.latent_dim,), "around_one"),
-                spec.k_up_weight: TensorRequest((spec.num_heads * spec.head_dim, spec.latent_dim)),
-                spec.v_up_weight: TensorRequest((spec.num_heads * spec.v_head_dim, spec.latent_dim)),
-                spec.o_weight: TensorRequest((spec.hidden_size, spec.num_heads * spec.v_head_dim))}
+        rope_dim = getattr(spec, "rope_dim", 0)
+        wanted = {spec.q_weight: TensorRequest((spec.num_heads * (spec.head_dim + rope_dim), spec.hidden_size)),
+                  spec.k_up_weight: TensorRequest((spec.num_heads * spec.head_dim, spec.latent_dim)),
+                  spec.v_up_weight: TensorRequest((spec.num_heads * spec.v_head_dim, spec.latent_dim)),
+                  spec.o_weight: TensorRequest((spec.hidden_size, spec.num_heads * spec.v_head_dim))}
+        if not getattr(spec, "shares_kv", False):
+            wanted[spec.down_weight] = TensorRequest((spec.latent_dim + rope_dim, spec.hidden_size))
+            wanted[spec.latent_norm] = TensorRequest((spec.latent_dim,), "around_one")
+        if getattr(spec, "sink", None) is not None:
+            wanted[spec.sink] = TensorRequest((spec.num_heads,))
+        if getattr(spec, "gate_weight", None) is not None:
+            wanted[spec.gate_weight] = TensorRequest((spec.num_heads, spec.hidden_size))
+        return wanted
 
     @classmethod
     def cache_request(cls, spec):
-        return CacheRequest("latent", 1, spec.latent_dim)
+        return CacheRequest("latent", 1, spec.latent_dim + getattr(spec, "rope_dim", 0))
 
     def bind(self, tensors):
         s = self.spec
-        parts = [self.rt.upload(tensors[s.q_weight]), self.rt.upload(tensors[s.down_weight])]
+        parts = [self.rt.upload(tensors[s.q_weight])]
+        if not self.shares_kv:
+            parts.append(self.rt.upload(tensors[s.down_weight]))
+        if self.has_gate:
+            parts.append(self.rt.upload(tensors[s.gate_weight]))
         rows = sum(part.shape[0] for part in parts)
         if rows < self.fused_width:                 # (zero rows: what they produce is never read)
             parts.append(parts[0].new_zeros(self.fused_width - rows, s.hidden_size))
         self.w_q_down = torch.cat(parts, dim=0).contiguous()
         del parts
-        self.latent_gamma = self.rt.upload(tensors[s.latent_norm], torch.float32)
+        self.latent_gamma = self.rt.upload(tensors[s.latent_norm], torch.float32) if not self.shares_kv else None
+        self.sink = (self.rt.upload(tensors[s.sink], torch.float32).reshape(-1).contiguous()
+                     if getattr(s, "sink", None) is not None else None)
         k_up = self.rt.upload(tensors[s.k_up_weight]).view(s.num_heads, s.head_dim, s.latent_dim)
         self.w_k_up_t = k_up.transpose(1, 2).contiguous()       # [heads, latent, head_dim]: q -> q in latent space
         self.w_v_up = self.rt.upload(tensors[s.v_up_weight]).view(s.num_heads, s.v_head_dim, s.latent_dim).contiguous()
         # keys' and values' up-projections as one matrix, for steps that make every head's keys and values
-        self.w_kv_up = torch.cat([self.rt.upload(tensors[s.k_up_weight]), self.rt.upload(tensors[s.v_up_weight])],
-                                 dim=0).contiguous()
+        self.w_kv_up = (torch.cat([self.rt.upload(tensors[s.k_up_weight]), self.rt.upload(tensors[s.v_up_weight])],
+                                  dim=0).contiguous() if not self.extended else None)
         w_o = self.rt.upload(tensors[s.o_weight])
         if self.ctx_width != self.ctx_dim:
             w_o = torch.cat([w_o, w_o.new_zeros(s.hidden_size, self.ctx_width - self.ctx_dim)], dim=1)
@@ -86,6 +125,11 @@ class LatentAttention(Mixer):
         group = step.cache.entry_group_index(cache_entry)
         table = step.block_tables[group]
         block_size = step.cache.block_size
+        if self.extended:
+            self._forward_extended(step, fused, latents, table, writes_cache)
+            ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+            ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
+            return
         q = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
         # queries pass as they are; the one "key head" of a row is the latent, normed with its weight and cached
         ops.qkv_finish(fused, q, latents, None, step.positions, step.token_seq, table, s.num_heads, 1, s.head_dim, 0,
@@ -95,6 +139,30 @@ class LatentAttention(Mixer):
         if not self._attend_expanded(step, q, ctx, latents, table, group):
             self._attend_folded(step, q, ctx, latents, table)
         ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
+
+    def _forward_extended(self, step, fused, cached, table, writes_cache):
+        """The folded way with a rotated part, a sink and a gate: finish the projection's rows (the latent's norm, the
+        rotations, the cache write), fold the keys' up-projection into the unrotated queries, attend with all heads
+        over the cached rows, apply the values' up-projection."""
+        s, rt = self.spec, self.rt
+        ops = rt.kernels()
+        n = fused.shape[0]
+        q_plain = rt.workspace.get("q", (n, s.num_heads * s.head_dim), rt.dtype)
+        q_folded = rt.workspace.get("q_latent", (n, s.num_heads * self.key_dim), rt.dtype)
+        rotation = self.position.fusion_table(step.max_ctx) if self.position is not None else None
+        ops.latent_finish(fused, q_plain, q_folded, cached, step.positions, step.token_seq, table, s.num_heads,
+                          s.head_dim, self.rope_dim, s.latent_dim, step.cache.block_size,
+                          rotation=rotation, rotated=s.rope.dims if rotation is not None else 0,
+                          latent_offset=self.q_dim, latent_gamma=self.latent_gamma, eps=s.eps,
+                          write_cache=writes_cache and not self.shares_kv)
+        ops.headwise_linear(q_plain, self.w_k_up_t, q_folded, s.num_heads, out_head_stride=self.key_dim)
+        mixed = rt.workspace.get("latent_ctx", (n, s.num_heads * s.latent_dim), rt.dtype)
+        ops.attention_general(q_folded, cached, cached, table, step.positions, step.token_seq, mixed, s.num_heads, 1,
+                              self.key_dim, s.latent_dim, step.cache.block_size, s.scale,
+                              gate=fused[:, self.gate_offset:] if self.has_gate else None, gate_stride=self.fused_width,
+                              sink=self.sink, value_stride=self.key_dim)
+        ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+        ops.headwise_linear(mixed, self.w_v_up, ctx, s.num_heads, zero_pad=self.ctx_width != self.ctx_dim)
 
     def _attend_folded(self, step, q, ctx, latents, table):
         """The up-projections folded into queries and outputs; attention of all heads over the cached vectors."""

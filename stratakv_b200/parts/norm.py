@@ -18,10 +18,14 @@ class RMSNorm(Norm):
 
     @classmethod
     def expected_tensors(cls, spec):
-        return {spec.weight: TensorRequest((spec.size,), "around_one")}
+        around_zero = bool(getattr(spec, "weight_offset", 0.0))
+        return {spec.weight: TensorRequest((spec.size,), "normal" if around_zero else "around_one")}
 
     def bind(self, tensors):
         self.gamma = self.rt.upload(tensors[self.spec.weight], torch.float32)
+        offset = getattr(self.spec, "weight_offset", 0.0)
+        if offset:                                    # (a weight stored as its distance from one)
+            self.gamma = (self.gamma + offset).contiguous()
 
     def forward(self, x, rows=None, out=None, name="normed", stats=None):
         """``stats`` prepared for this norm: leave the rest of the work to the consumer's projection."""

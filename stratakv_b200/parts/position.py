@@ -9,6 +9,8 @@ for; the kernel that applies it also writes keys and values into the cache.
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -81,5 +83,54 @@ class NoPosition:
             num_heads, num_kv_heads, head_dim, block_size, write_kv)
 
 
+def rotary_table(spec, positions: int) -> np.ndarray:
+    """``[positions, dims/2, 2]`` float32 of (cos, sin) for a ``RotarySpec``: frequencies and angles in double, the
+    stretch of the frequencies (``YarnSpec``) and its factor on cosines and sines included, rounded to float last."""
+    dims, base = spec.dims, float(spec.base)
+    half = dims // 2
+    index = np.arange(half, dtype=np.float64)
+    freq = np.power(np.float64(base), -2.0 * index / float(dims))
+    magnitude = 1.0
+    scaling = spec.scaling
+    if scaling is not None:
+        def pair_of(turns):
+            return dims * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+        lo = max(math.floor(pair_of(scaling.fast)), 0)
+        hi = min(math.ceil(pair_of(scaling.slow)), dims - 1)
+        ramp = np.clip((index - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        freq = freq / scaling.factor * ramp + freq * (1.0 - ramp)
+        magnitude = 0.1 * math.log(scaling.factor) + 1.0
+    angle = np.arange(positions, dtype=np.float64)[:, None] * freq[None, :]
+    return (np.stack([np.cos(angle), np.sin(angle)], axis=-1) * magnitude).astype(np.float32)
+
+
+class RotaryTable:
+    """A (cos, sin) table for rotations over part of a vector, with or without stretched frequencies; the mixers
+    that use it hand ``table`` and ``spec.dims`` to their kernels."""
+    role = "position"
+
+    def __init__(self, spec, runtime):
+        self.spec = spec
+        self.rt = runtime
+        self.table = None
+        self.length = 0
+        self._retired = []          # earlier tables stay alive: captured graphs may still read them
+
+    def ensure(self, positions: int) -> None:
+        """Make the table cover positions ``0 .. positions-1`` (never inside a graph capture)."""
+        if positions <= self.length:
+            return
+        length = max(positions, 2 * self.length, 256)
+        if self.table is not None:
+            self._retired.append(self.table)
+        self.table = torch.from_numpy(rotary_table(self.spec, length)).to(self.rt.device).contiguous()
+        self.length = length
+
+    def fusion_table(self, max_positions: int):
+        self.ensure(max_positions)
+        return self.table
+
+
+register_position("rotary_table", RotaryTable)
 register_position("rope_half", RopeHalf)
 register_position("none", NoPosition)

@@ -10,7 +10,7 @@ from typing import Dict
 
 _KINDS: Dict[str, Dict[str, type]] = {"mixer": {}, "ffn": {}, "norm": {}, "position": {},
                                       "arrangement": {}, "embedding": {}, "head": {},
-                                      "token_input": {}}
+                                      "token_input": {}, "stream_mix": {}}
 
 
 def register_part(role: str, kind: str, cls) -> None:
@@ -27,6 +27,7 @@ def register_arrangement(kind, fn): register_part("arrangement", kind, fn)
 def register_embedding(kind, cls): register_part("embedding", kind, cls)
 def register_head(kind, cls): register_part("head", kind, cls)
 def register_token_input(kind, cls): register_part("token_input", kind, cls)
+def register_stream_mix(kind, cls): register_part("stream_mix", kind, cls)
 
 
 def part_class(role: str, kind: str):

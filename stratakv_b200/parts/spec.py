@@ -20,6 +20,9 @@ class NormSpec:
     eps: float
     weight: str                      # tensor name
     kind: str = "rmsnorm"
+    # added to the stored weight when it is loaded: 1.0 for checkpoints that keep a norm's weight as its distance
+    # from one (``y = x / rms * (1 + w)``)
+    weight_offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -28,6 +31,29 @@ class RopeSpec:
     head_dim: int
     theta: float
     kind: str = "rope_half"
+
+
+@dataclass(frozen=True)
+class YarnSpec:
+    """Rotary frequencies stretched for contexts longer than the ``original`` one (YaRN).  With
+    ``pair(t) = dims ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(pair(fast)), 0)``,
+    ``hi = min(ceil(pair(slow)), dims - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, pair i turns
+    at ``f_i / factor * ramp_i + f_i (1 - ramp_i)``, and cosines and sines are multiplied by ``0.1 ln(factor) + 1``."""
+    factor: float
+    original: int
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
+class RotarySpec:
+    """Rotary positions on the first ``dims`` numbers of a vector (the rest pass), number i paired with number
+    ``i + dims/2``: ``(u, v) -> (u cos a - v sin a, v cos a + u sin a)``, ``a = position * base^(-2i/dims)``;
+    ``scaling`` changes the frequencies (``YarnSpec``)."""
+    dims: int
+    base: float
+    scaling: Optional[YarnSpec] = None
+    kind: str = "rotary_table"
 
 
 @dataclass(frozen=True)
@@ -105,7 +131,15 @@ class LatentAttentionSpec:
 
     ``c = rmsnorm(Wdkv h) * latent_norm`` (``latent_dim`` numbers) is all the cache keeps; head h has
     ``k = Wuk[h] c`` (``head_dim``) and ``v = Wuv[h] c`` (``v_head_dim``), ``score = (q . k) * scale``, no position
-    encoding; ``x += Wo (heads' outputs)``."""
+    encoding; ``x += Wo (heads' outputs)``.
+
+    Mechanisms a design may add, each off by default.  ``rope_dim`` r > 0 with ``rope``: a query head is
+    ``[head_dim unrotated | r rotated]`` numbers, the down projection has r more rows, which (not normed, rotated) are
+    one key part that all heads share and that is cached behind the latent; the score adds the two parts' products.
+    ``sink``: a learned number per head whose exponential counts once in the softmax's denominator (no key, no value,
+    not scaled).  ``gate_weight`` ``[heads, hidden]``: a head's output times ``sigmoid(gate_weight[head] . h)``.
+    ``shares_kv``: no down projection of its own; the layer attends over the cache entry another layer's run wrote
+    (its schedule entry names that entry and does not write it)."""
     hidden_size: int
     num_heads: int
     head_dim: int
@@ -120,6 +154,32 @@ class LatentAttentionSpec:
     v_up_weight: str                 # [heads * v_head_dim, latent_dim]
     o_weight: str                    # [hidden, heads * v_head_dim]
     kind: str = "latent_attention"
+    rope_dim: int = 0
+    rope: Optional[RotarySpec] = None
+    sink: Optional[str] = None            # [heads]
+    gate_weight: Optional[str] = None     # [heads, hidden]
+    shares_kv: bool = False
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head and no softmax: ``q, k = rot(Wq h), rot(Wk h) * head_dim^-1/2``,
+    ``v = Wv h``; per head ``S_t = decay S_(t-1) + k_t v_t^T`` (``head_dim x v_head_dim`` floats a sequence keeps),
+    ``o_t = S_t^T q_t``; every head of o divided by its root mean square (``eps``), the heads times
+    ``silu(Wg h)``, then ``Wo``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    v_head_dim: int
+    decay: Tuple[float, ...]         # per head
+    eps: float
+    rope: Optional[RotarySpec]
+    q_weight: str                    # [heads * head_dim, hidden]
+    k_weight: str
+    v_weight: str                    # [heads * v_head_dim, hidden]
+    gate_weight: str                 # [heads * v_head_dim, hidden]
+    o_weight: str                    # [hidden, heads * v_head_dim]
+    kind: str = "retention"
 
 
 @dataclass(frozen=True)
@@ -190,6 +250,48 @@ class MlpSpec:
 
 
 @dataclass(frozen=True)
+class SharedExpertSpec:
+    """An expert every token uses; ``gate_weight`` ``[1, hidden]``: its result times ``sigmoid(gate_weight . h)``."""
+    intermediate_size: int
+    up_weight: str
+    down_weight: str
+    gate_weight: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class RoutedMlpSpec:
+    """A mixture of ``experts`` feed-forwards ``down_e act(up_e h)`` of which a token uses ``top``: router scores
+    ``s = sigmoid(router h)`` in float32; the ``top`` largest ``s + correction`` choose; the chosen experts' results
+    are added with weights ``s * route_scale`` (``renormalize``: divided by their sum first).  ``up_weights`` and
+    ``down_weights`` name one tensor per expert."""
+    hidden_size: int
+    intermediate_size: int
+    experts: int
+    top: int
+    activation: str
+    route_scale: float
+    router_weight: str               # [experts, hidden]
+    up_weights: Tuple[str, ...]      # each [intermediate, hidden]
+    down_weights: Tuple[str, ...]    # each [hidden, intermediate]
+    correction: Optional[str] = None # [experts], added to the scores that choose only
+    renormalize: bool = False
+    shared: Optional[SharedExpertSpec] = None
+    kind: str = "routed_mlp"
+
+
+@dataclass(frozen=True)
+class StreamMixSpec:
+    """How one sublayer is connected to ``streams`` copies of the residual stream (hyper-connections): it reads
+    ``sum_s read[s] x_s``, and every stream becomes ``x_t <- sum_s mix[s, t] x_s + write[t] * result``, all from the
+    old ones.  Without tensor names the connection is the plain residual sum (read 1, mix 1, write 1)."""
+    streams: int
+    read: Optional[str] = None       # [streams]
+    write: Optional[str] = None      # [streams]
+    mix: Optional[str] = None        # [streams, streams], indexed [from, to]
+    kind: str = "stream_mix"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which norm, mixer and feed-forward, and how they are arranged.
 
@@ -200,6 +302,8 @@ class LayerSpec:
     ``sandwich``: ``x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x)))``, then ``token_input`` if the layer
     has one; the norms after the sublayers are the extras ``mixer_post_norm`` and ``ffn_post_norm``, ``ffn`` (with
     its two norms) may be ``None``.
+    ``multi_stream``: the ``pre_norm`` block over several copies of the stream; the extras ``mixer_streams`` and
+    ``ffn_streams`` (``StreamMixSpec``) say how each sublayer reads and writes them; ``ffn`` may be ``None``.
 
     The four named places are what that arrangement uses; another arrangement may leave
     some of them ``None`` (a block without a feed-forward, one norm for two branches) and

@@ -157,7 +157,7 @@ class DoubleKernels:
 
     def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads, num_kv_heads,
                           dim, vdim, block_size, scale, window=0, r1=None, r2=None, gate=None, gate_stride=0,
-                          softcap=0.0, gate_per_element=False):
+                          softcap=0.0, gate_per_element=False, sink=None, value_stride=0):
         self.calls.append("attention_general")
         n = q.shape[0]
         group = num_heads // num_kv_heads
@@ -168,7 +168,7 @@ class DoubleKernels:
             lo = max(0, pos - window + 1) if window > 0 else 0
             where = [(int(block_table[seq, j // block_size]), j % block_size) for j in range(lo, pos + 1)]
             keys = torch.stack([k_cache[b, :, r, :] for b, r in where]).float()
-            values = torch.stack([v_cache[b, :, r, :] for b, r in where]).float()
+            values = torch.stack([v_cache[b, :, r, :vdim] for b, r in where]).float()
             distance = torch.arange(pos - lo, -1, -1, dtype=torch.float32)
             for h in range(num_heads):
                 score = (keys[:, h // group, :] @ qh[t, h]) * scale
@@ -176,7 +176,10 @@ class DoubleKernels:
                     score = score - r1[h] * torch.log1p(r2[h] * distance)
                 if softcap > 0.0:
                     score = softcap * torch.tanh(score / softcap)
-                result = torch.softmax(score, dim=0) @ values[:, h // group, :]
+                if sink is not None:                # one more term in the denominator, with no value
+                    result = torch.softmax(torch.cat([score, sink[h].view(1)]), dim=0)[:-1] @ values[:, h // group, :]
+                else:
+                    result = torch.softmax(score, dim=0) @ values[:, h // group, :]
                 if gate is not None and gate_per_element:
                     result = result * torch.sigmoid(gate[t, h * vdim:(h + 1) * vdim])
                 elif gate is not None:
@@ -198,13 +201,137 @@ class DoubleKernels:
         g = torch.nn.functional.gelu(x @ gate_w.float().T, approximate="tanh") * e
         self.rmsnorm_add(g @ proj_t.float(), norm_w, eps, x, next_gamma, next_eps, next_out)
 
-    def headwise_linear(self, x, w, out, heads, zero_pad=False):
+    def headwise_linear(self, x, w, out, heads, zero_pad=False, out_head_stride=0):
         self.calls.append("headwise_linear")
         n, out_dim, in_dim = x.shape[0], w.shape[1], w.shape[2]
         parts = x[:, :heads * in_dim].float().view(n, heads, in_dim)
         if zero_pad:
             out.zero_()
-        out[:, :heads * out_dim] = torch.einsum("thi,hoi->tho", parts, w.float()).reshape(n, heads * out_dim).to(out.dtype)
+        result = torch.einsum("thi,hoi->tho", parts, w.float()).to(out.dtype)
+        if out_head_stride and out_head_stride != out_dim:
+            for h in range(heads):
+                out[:, h * out_head_stride:h * out_head_stride + out_dim] = result[:, h]
+        else:
+            out[:, :heads * out_dim] = result.reshape(n, heads * out_dim)
+
+    def stream_mix(self, streams, count, source=None, branch=None, mix=None, write=None, read=None, gamma=None,
+                   eps=0.0, normed_out=None, sum_out=None):
+        self.calls.append("stream_mix")
+        old = streams.clone() if source is None else source[None].repeat(count, 1, 1)
+        if branch is not None:
+            old = torch.einsum("sr,stw->rtw", mix.view(count, count), old) + write[:, None, None] * branch[None]
+            streams.copy_(old)
+        if normed_out is not None:
+            u = torch.einsum("s,stw->tw", read, old)
+            normed_out.copy_((u / torch.sqrt((u * u).mean(dim=-1, keepdim=True) + eps) * gamma).to(normed_out.dtype))
+        if sum_out is not None:
+            sum_out.copy_(old.sum(dim=0))
+
+    def retention_scratch(self, n_seqs, max_q_len, heads, dim, vdim):
+        return 0
+
+    @staticmethod
+    def _turn(x, cos_sin, positions, rotated):
+        """x [n, ..., width]: the first ``rotated`` numbers of the last axis turned by the table's angles."""
+        if cos_sin is None or rotated == 0:
+            return x
+        half = rotated // 2
+        cs = cos_sin[positions.long()]
+        shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (half,)
+        c, s = cs[:, :, 0].view(shape), cs[:, :, 1].view(shape)
+        u, v = x[..., :half], x[..., half:rotated]
+        return torch.cat([u * c - v * s, v * c + u * s, x[..., rotated:]], dim=-1)
+
+    def retention(self, fused, cos_sin, rotated, decay, eps, out, state, step_meta, heads, dim, vdim, max_q_len, scratch=None):
+        self.calls.append("retention")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        n = fused.shape[0]
+        a, b = heads * dim, heads * vdim
+        q = self._turn(fused[:, :a].view(n, heads, dim), cos_sin, positions, rotated)
+        k = self._turn(fused[:, a:2 * a].view(n, heads, dim), cos_sin, positions, rotated) * dim ** -0.5
+        v = fused[:, 2 * a:2 * a + b].view(n, heads, vdim)
+        gate = fused[:, 2 * a + b:2 * a + 2 * b]
+        size = heads * dim * vdim
+        out.zero_()
+        for s in range(slot_ids.numel()):
+            first, last = int(cu_q[s]), int(cu_q[s + 1]) - 1
+            row = state[int(slot_ids[s])]
+            p_first = int(positions[first])
+            S = (row[((p_first - 1) & 1) * size:][:size].clone().view(heads, dim, vdim) if p_first > 0
+                 else torch.zeros(heads, dim, vdim))
+            for t in range(first, last + 1):
+                S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+                o = torch.einsum("hde,hd->he", S, q[t])
+                o = o / torch.sqrt((o * o).mean(dim=-1, keepdim=True) + eps)
+                out[t, :b] = (o.reshape(b) * gate[t] * torch.sigmoid(gate[t])).to(out.dtype)
+            row[((p_first + last - first) & 1) * size:][:size] = S.reshape(size)
+
+    def latent_finish(self, fused, q_plain, q_folded, cache, positions, token_seq, block_table, heads, dim, rope_dim,
+                      latent_dim, block_size, rotation=None, rotated=0, latent_offset=0, latent_gamma=None, eps=0.0,
+                      write_cache=True):
+        self.calls.append("latent_finish")
+        n, key_dim = fused.shape[0], latent_dim + rope_dim
+        q = fused[:, :heads * (dim + rope_dim)].view(n, heads, dim + rope_dim)
+        q_plain.copy_(q[:, :, :dim].reshape(n, heads * dim).to(q_plain.dtype))
+        if rope_dim:
+            turned = self._turn(q[:, :, dim:], rotation, positions, rotated)
+            q_folded.view(n, heads, key_dim)[:, :, latent_dim:] = turned.to(q_folded.dtype)
+        if not write_cache:
+            return
+        c = fused[:, latent_offset:latent_offset + latent_dim]
+        c = c / torch.sqrt((c * c).mean(dim=-1, keepdim=True) + eps) * latent_gamma
+        rows = torch.cat([c, self._turn(fused[:, latent_offset + latent_dim:latent_offset + key_dim], rotation, positions,
+                                        rotated)], dim=-1)
+        for t in range(n):
+            pos = int(positions[t])
+            block = int(block_table[int(token_seq[t]), pos // block_size])
+            cache[block, 0, pos % block_size, :] = rows[t].to(cache.dtype)
+
+    def route_tokens(self, h, router_w, correction, top, scale, renormalize, chosen, weights, shared_gate_weight=None,
+                     shared_gate_out=None):
+        self.calls.append("route_tokens")
+        s = torch.sigmoid(h.float() @ router_w.float().T)
+        choice = s + correction if correction is not None else s
+        picked = torch.topk(choice, top, dim=-1).indices
+        w = torch.gather(s, 1, picked)
+        if renormalize:
+            w = w / w.sum(dim=-1, keepdim=True)
+        chosen.copy_(picked.to(torch.int32))
+        weights.copy_(w * scale)
+        if shared_gate_out is not None:
+            shared_gate_out.copy_(torch.sigmoid(h.float() @ shared_gate_weight.float()))
+
+    def sort_by_expert(self, chosen, experts, offsets, order, place):
+        self.calls.append("sort_by_expert")
+        flat = chosen.reshape(-1).long()
+        sorted_pairs = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=experts)
+        offsets[0] = 0
+        offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        order.copy_((sorted_pairs // chosen.shape[1]).to(torch.int32))
+        place.view(-1)[sorted_pairs] = torch.arange(flat.numel(), dtype=torch.int32)
+
+    def expert_linear(self, a, w, offsets, out, rows=None, activation=None):
+        self.calls.append("expert_linear")
+        for e in range(w.shape[0]):
+            lo, hi = int(offsets[e]), int(offsets[e + 1])
+            if hi == lo:
+                continue
+            src = a[rows[lo:hi].long()] if rows is not None else a[lo:hi]
+            result = src.float() @ w[e].float().T
+            if activation is not None:
+                result = ACTIVATIONS[activation](result)
+            out[lo:hi] = result.to(out.dtype)
+
+    def combine_experts(self, results, place, weights, shared, share, x, add=True):
+        self.calls.append("combine_experts")
+        total = (results[place.long()] * weights[:, :, None]).sum(dim=1)
+        if shared is not None:
+            total = total + (shared * share[:, None] if share is not None else shared)
+        if add:
+            x.add_(total)
+        else:
+            x.copy_(total)
 
     def rglru_conv(self, yx, x_offset, x_bias, conv_w, conv_b, u, step_meta, state):
         self.calls.append("rglru_conv")
