@@ -4,6 +4,8 @@
     python bench.py --design zepavik [--layers 8]       (the Zepavik decoder beside Llama at equal layer sizes)
     python bench.py --design povusun [--layers 8]       (the Povusun decoder beside Llama: mixed layers, and each of its
                                                          three mixers alone)
+    python bench.py --design kedelorn [--layers 8]      (the Kedelorn decoder beside Llama and beside Povusun's latent and
+                                                         recurrent layers: mixed layers, and each of its two mixers alone)
 
 The default run has the layer sizes of the TinyLlama-1.1B shape (22 layers,
 hidden 2048, 32 heads, 4 KV heads, head size 64, feed-forward 5632, vocabulary
@@ -243,10 +245,103 @@ def povusun_arm(args) -> int:
     return 0
 
 
+def kedelorn_config(size, layers, vocab, kinds, streams=2):
+    """A Kedelorn configuration at a size of DESIGN_SIZES whose layer i has the mixer ``kinds[i % len(kinds)]``.  The
+    retention layers have Llama's heads with keys and values of the head size, the whole head rotated, and decays
+    from 1 - 2^-5 to 1 - 2^-8.  The latent layers have Llama's heads, an unrotated part of the head size and a rotated
+    one of half of it with stretched frequencies, a latent of four heads' width (at most 256) as the Povusun arm has,
+    a sink and a gate; where the mix has latent layers, every second of them attends over the one before.  The
+    feed-forward has eight experts of which two, and a shared one, each half as wide as Llama's: a token passes
+    through as many feed-forward weights as in Llama (two matrices an expert, three there)."""
+    from stratakv_b200.config import KedelornConfig
+    d, heads, made, latents = size["head_dim"], size["heads"], [], []
+    expert_ff = size["llama_ff"] // 2 // 64 * 64
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": 8, "top": 2, "scale": 1.0},
+           "shared": {"ff": expert_ff}}
+    for i in range(layers):
+        kind = kinds[i % len(kinds)]
+        if kind == "retention":
+            mixer = {"heads": heads, "dim": d, "vdim": d, "rot": {"dims": d, "base": 10000.0},
+                     "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(heads - 1, 1)) for h in range(heads)]}
+        else:
+            mixer = {"heads": heads, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": min(256, 4 * d), "scale": (1.5 * d) ** -0.5,
+                     "rot": {"dims": d // 2, "base": 10000.0,
+                             "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+            if len(latents) % 2 == 1:
+                mixer["kv_from"] = latents[-1]
+            latents.append(i)
+        made.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    raw = {"architecture": "Kedelorn", "vocab": vocab, "width": size["hidden"], "norm": {"eps": 1e-5}, "layers": made}
+    if streams:
+        raw["streams"] = streams
+    return KedelornConfig.from_dict(raw)
+
+
+def kedelorn_arm(args) -> int:
+    """Prefill and decode of the Kedelorn decoder beside the Llama decoder and beside the Povusun decoder's latent and
+    recurrent layers (the framework's nearest kernels) at equal layer sizes, random weights: a model that mixes its
+    two kinds of layer, and one of each kind alone."""
+    import gc
+    import torch
+    from stratakv_b200.config import LlamaConfig
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    layers, vocab, context, batch = args.layers or 8, 32000, args.context, args.batch
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    peak = peaks()
+    sizes = {}
+    sampler = ClockSampler()
+    sampler.start()
+    for name, size in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        configs = {"llama": LlamaConfig.from_dict(dict(
+            TINYLLAMA, hidden_size=size["hidden"], intermediate_size=size["llama_ff"], num_hidden_layers=layers,
+            num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"],
+            vocab_size=vocab, max_position_embeddings=context + 64)),
+            "povusun_latent_only": povusun_config(size, layers, vocab, ("latent_attention",)),
+            "povusun_rglru_only": povusun_config(size, layers, vocab, ("rglru",)),
+            "kedelorn": kedelorn_config(size, layers, vocab, ("retention", "latent_attention")),
+            "kedelorn_latent_only": kedelorn_config(size, layers, vocab, ("latent_attention",)),
+            "kedelorn_retention_only": kedelorn_config(size, layers, vocab, ("retention",))}
+        only = [label for label in args.arms.split(",") if label] if args.arms else list(configs)
+        row = {}
+        for label in only:
+            config = configs[label]
+            engine = engine_of(config, max(batch * (context + 64), PREFILL_TOKENS + 64), batch)
+            prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+            decode_ms, launches, _ = time_decode(engine, batch, context - steps - warmup, steps, warmup, vocab)
+            weight_bytes = engine.model.weight_bytes()
+            kv_bytes = batch * context * engine.cache.bytes_per_token()
+            row[label] = {"prefill_tokens_per_s": PREFILL_TOKENS * 1000.0 / prefill_ms, "prefill_ms": prefill_ms,
+                          "decode_tokens_per_s": batch * 1000.0 / decode_ms, "decode_ms_per_step": decode_ms,
+                          "decode_hbm_frac": (weight_bytes + kv_bytes) / (decode_ms * 1e-3) / 1e9 / peak["hbm_gbs"],
+                          "weight_bytes": weight_bytes, "cache_bytes_per_token": engine.cache.bytes_per_token(),
+                          "launches_in_timed_steps": launches}
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        if "llama" in row:
+            for label in row:
+                row[label]["prefill_ratio"] = row[label]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"]
+                row[label]["decode_ratio"] = row[label]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"]
+        sizes[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "Kedelorn", "beside": ["LlamaForCausalLM", "Povusun"], "layers": layers, "vocab": vocab,
+                      "prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context, "dtype": "bf16",
+                      "steps": steps, "warmup": warmup,
+                      "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "peaks": peak,
+                      "clocks": clocks, "sizes": sizes}))
+    return 0
+
+
 def design_arm(args) -> int:
     """Prefill and decode of the Zepavik decoder and of the Llama decoder at equal layer sizes (random weights)."""
     if args.design == "povusun":
         return povusun_arm(args)
+    if args.design == "kedelorn":
+        return kedelorn_arm(args)
     import gc
     import torch
     from stratakv_b200.config import LlamaConfig, ZepavikConfig
@@ -596,9 +691,10 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context at which the timed decode steps end")
-    parser.add_argument("--design", choices=["zepavik", "povusun"],
+    parser.add_argument("--design", choices=["zepavik", "povusun", "kedelorn"],
                         help="measure this design beside the Llama decoder at equal layer sizes instead of the step benchmark")
     parser.add_argument("--sizes", default="", help="with --design: names of DESIGN_SIZES, with commas (default: all)")
+    parser.add_argument("--arms", default="", help="with --design kedelorn: which models to time, with commas (default: all)")
     parser.add_argument("--window", type=int, default=0, help="with --design: the design's window (default: the whole context)")
     parser.add_argument("--workload", choices=sorted(WORKLOADS),
                         help="a whole generation workload through Engine.generate instead of the step benchmark")

@@ -241,7 +241,8 @@ class Engine:
         """Run one step.  Returns float32 logits ``[wanted, vocab]`` on the device,
         in the order of the entries and of their ``want`` (``None`` when nothing
         is wanted).  The tensor is scratch memory: use or copy it before the next step."""
-        if self._use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
+        probed = self.model.layer_probe is not None or self.model.choice_probe is not None
+        if self._use_graphs and not probed and entries and all(len(e.tokens) == 1 for e in entries):
             return self._decode_step(entries)
         step, want_rows, n_want = self.prepare(entries)
         logits = self.model.forward(step, want_rows, n_want)

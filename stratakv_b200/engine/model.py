@@ -90,6 +90,10 @@ class Model:
         # A callable ``(run index, stream)`` that sees the float32 residual stream after every run of a layer (for
         # tests and for finding the layer where two implementations part); None in service.
         self.layer_probe = None
+        # A callable ``(run index, step, chosen)`` that sees which experts a routed feed-forward chose for the step's
+        # tokens (``[tokens, top]`` int32 on the device), for telling a router's close call from a fault; None in
+        # service.  A step with a probe does not run as a graph.
+        self.choice_probe = None
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.embedding.bind(tensors)
@@ -139,6 +143,7 @@ class Model:
             # few rows: norms are folded into the projections after them (residual.py)
             stats = ResidualStats.allocate(rt.workspace.get, step.n_tokens, spec.hidden_size, rt.dtype)
         step.residual_stats = stats
+        step.choice_probe = self.choice_probe
         final = self.final_norm if self.final_norm.folds_norm and self.head.folds_norm else None
         readers = [self.layers[entry.layer].first_norm for entry in spec.schedule] + [final]
         if stats is not None:

@@ -127,6 +127,7 @@ class StepBatch:
     # True while a part is handed a scratch buffer in place of the stream and is to STORE its result there instead
     # of adding it (an arrangement that norms a sublayer's output sets it for parts with ``stores_branch``)
     store_branch: bool = False
+    choice_probe: Any = None           # a callable that is shown the experts a routed feed-forward chose (tests)
 
     @property
     def is_decode(self) -> bool:

@@ -95,6 +95,8 @@ class RoutedMlp(FeedForward):
         share = get("routed_share", (n,), torch.float32) if self.shared_gate is not None else None
         ops.route_tokens(h, self.w_router, self.correction, s.top, s.route_scale, s.renormalize, chosen, weights,
                          shared_gate_weight=self.shared_gate, shared_gate_out=share)
+        if step.choice_probe is not None:
+            step.choice_probe(step.run_index, step, chosen)
         offsets = get("routed_offsets", (s.experts + 1,), torch.int32)
         order = get("routed_order", (pairs,), torch.int32)           # the token of every sorted pair
         place = get("routed_place", (n, s.top), torch.int32)         # where each (token, choice) went

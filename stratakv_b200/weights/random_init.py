@@ -34,7 +34,7 @@ def random_tensor(name: str, request: TensorRequest, seed: int, std: float,
     elif request.init == "positive":           # numbers of order one above zero (slopes, rates)
         values = values.abs() / std * 0.5 + 0.05
     elif request.init == "around_identity":    # a square matrix that mixes a little
-        values += torch.eye(request.shape[0], request.shape[1])
+        values += torch.eye(request.shape[0], request.shape[1], device=device)
     elif request.init != "normal":
         raise ValueError(f"unknown init '{request.init}' for tensor {name}")
     return values.to(dtype)

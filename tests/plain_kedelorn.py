@@ -119,16 +119,49 @@ def expert(h, up, down):
     return torch.relu(h @ up.T) ** 2 @ down.T
 
 
-def route(h, P, p, mlp):
-    """Which experts each token uses, and with which weights: [T, top] indices and [T, top] weights."""
+# Choice scores nearer than this are a close call for an implementation in bfloat16: the router reads a normed stream
+# that carries the rounding of every layer before it (a few hundredths of its spread in the test models), through
+# rows of the router's matrix whose length is two to three, and the sigmoid's slope is at most a quarter.
+CLOSE_CALL = 0.08
+# (layer prefix, token, distance from a tie) of the proposals since the last forward that differed from the choice
+# here by more than a close call; they are followed all the same, and the caller decides how many it accepts
+FAR_CALLS = []
+DECISIONS = [0]          # how many tokens' choices were compared with a proposal since the last forward
+
+
+def route(h, P, p, mlp, proposed=None):
+    """Which experts each token uses, and with which weights: [T, top] indices and [T, top] weights.
+
+    ``proposed`` ([T, top] indices, -1 where nothing is proposed) is another implementation's choice, which is followed:
+    where two choice scores are nearer than the other implementation's rounding, either choice is right, and everything
+    after it has to be compared along the same path.  A proposal that differs by more than CLOSE_CALL (its weakest
+    expert that far below the last chosen one's score, or an expert it leaves out that far above) is noted in
+    FAR_CALLS: a router that works has few of them, one that leaves out the correction or the sigmoid has many."""
     router = mlp["router"]
     s = torch.sigmoid(h @ P[p + "mlp.router"].T)
-    chosen = torch.topk(s + P[p + "mlp.correction"], router["top"], dim=-1).indices
+    choice = s + P[p + "mlp.correction"]
+    best = torch.topk(choice, router["top"], dim=-1)
+    chosen = best.indices.clone()
+    if proposed is not None:
+        for t in range(h.shape[0]):
+            theirs = [int(e) for e in proposed[t]]
+            if min(theirs) < 0 or len(set(theirs)) != len(theirs) or max(theirs) >= s.shape[1]:
+                continue
+            DECISIONS[0] += 1
+            if set(theirs) == set(best.indices[t].tolist()):
+                continue
+            edge = float(best.values[t, -1])
+            # how far from a tie the proposal is: its weakest expert below the edge, the strongest one it leaves out above
+            below = edge - min(float(choice[t, e]) for e in theirs)
+            above = max(float(choice[t, e]) for e in range(s.shape[1]) if e not in theirs) - edge
+            if max(below, above) > CLOSE_CALL:
+                FAR_CALLS.append((p, t, round(max(below, above), 4)))
+            chosen[t] = torch.tensor(theirs)
     return chosen, torch.gather(s, 1, chosen) * router["scale"]
 
 
-def moe(h, P, p, mlp):
-    chosen, weights = route(h, P, p, mlp)
+def moe(h, P, p, mlp, proposed=None):
+    chosen, weights = route(h, P, p, mlp, proposed)
     out = torch.zeros(h.shape[0], P[p + "mlp.e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t].tolist(), weights[t]):
@@ -147,10 +180,13 @@ def hyper_sublayer(streams, P, prefix, sublayer):
     return torch.einsum("sr,stw->rtw", P[prefix + ".mix"], streams) + P[prefix + ".out"][:, None, None] * y[None]
 
 
-def forward(cfg, P, tokens, layer_outputs=None):
+def forward(cfg, P, tokens, layer_outputs=None, proposed=None):
     """Logits [T, vocab] for one sequence of token ids; ``layer_outputs`` (a list) receives the sum of the streams
-    after every layer."""
+    after every layer.  ``proposed`` maps a layer's index to the experts another implementation chose there
+    ([T, top]; see ``route``)."""
     eps = cfg["norm"]["eps"]
+    FAR_CALLS.clear()
+    DECISIONS[0] = 0
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = P["embed"][tokens]
     n_streams = cfg.get("streams", 0)
@@ -168,7 +204,8 @@ def forward(cfg, P, tokens, layer_outputs=None):
             return latent_attention_mixer(h, P, p, m, eps, kept[m["kv_from"] if m.get("kv_from") is not None else i])
 
         def feed_forward(u):
-            return moe(norm_around_zero(u, P[p + "norm2"], eps), P, p, layer["mlp"])
+            return moe(norm_around_zero(u, P[p + "norm2"], eps), P, p, layer["mlp"],
+                       proposed.get(i) if proposed else None)
 
         if n_streams:
             streams = hyper_sublayer(streams, P, p + "hc1", mixer)
@@ -182,3 +219,28 @@ def forward(cfg, P, tokens, layer_outputs=None):
             layer_outputs.append(streams.sum(dim=0))
     x = streams.sum(dim=0)
     return norm_around_zero(x, P["final.norm"], eps) @ P["head"].T
+
+
+def load_folder(folder):
+    """(config dictionary, tensors as float64) of a model folder; reads the safetensors container itself."""
+    import json
+    import struct
+    from pathlib import Path
+    folder = Path(folder)
+    cfg = json.loads((folder / "config.json").read_text())
+    raw = (folder / "model.safetensors").read_bytes()
+    (size,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + size])
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "F16": torch.float16, "I32": torch.int32}
+    P = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        begin, end = info["data_offsets"]
+        flat = torch.frombuffer(bytearray(raw[8 + size + begin:8 + size + end]), dtype=kinds[info["dtype"]])
+        P[name] = flat.reshape(info["shape"]).to(F64)
+    return cfg, P
+
+
+def logits_of(cfg, P, tokens, proposed=None):
+    return forward(cfg, P, tokens, proposed=proposed)
