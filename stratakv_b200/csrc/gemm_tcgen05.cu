@@ -480,11 +480,43 @@ __device__ __forceinline__ void epilogue_tile_rope(uint32_t acc_tmem, int quarte
     }
 }
 
+// Grouped form (a routed feed-forward's experts): the rows of A are sorted by group, group e owning rows
+// offsets[e] .. offsets[e + 1], and W holds one [N, K] matrix per group, one after the other.  A row tile starts at a
+// group's first row and at every 128th after it, so no tile spans two groups: what a tile computes for rows past its
+// group's last (they belong to the next group, or lie past the matrix) is not stored.  The counts stay on the device.
+struct GroupArgs {
+    const int* offsets;                // [groups + 1], or null: the plain product
+    int groups;
+};
+
+__device__ __forceinline__ int group_row_tiles(const GroupArgs& group) {
+    int tiles = 0;
+    for (int e = 0; e < group.groups; ++e) tiles += (group.offsets[e + 1] - group.offsets[e] + TC_BM - 1) / TC_BM;
+    return tiles;
+}
+
+// Row tile `row_tile` of the grouped form: its first row, the row after its group's last, and its group.
+__device__ __forceinline__ void group_tile(const GroupArgs& group, int row_tile, int& m0, int& m_end, int& owner) {
+    int seen = 0;
+    m0 = 0; m_end = 0; owner = 0;
+    for (int e = 0; e < group.groups; ++e) {
+        const int lo = group.offsets[e], hi = group.offsets[e + 1];
+        const int tiles = (hi - lo + TC_BM - 1) / TC_BM;
+        if (row_tile < seen + tiles) {
+            m0 = lo + (row_tile - seen) * TC_BM;
+            m_end = hi;
+            owner = e;
+            return;
+        }
+        seen += tiles;
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_out, int tma_out, void* __restrict__ out, int M,
-                    int N, int K, int mode, act_t act, int* __restrict__ flag, const RopeArgs rope) {
+                    int N, int K, int mode, act_t act, int* __restrict__ flag, const RopeArgs rope, const GroupArgs group) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, W_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + W_BYTES;
     // tensor memory is handed out in powers of two columns: two accumulators, each at the start of a half
     constexpr uint32_t TMEM_COLS = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512), ACC_STRIDE = TMEM_COLS / 2;
@@ -498,9 +530,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_iters = (K + TC_BK - 1) / TC_BK;
-    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
-    const int total_tiles = m_tiles * n_tiles;
+    const int n_tiles = (N + BN - 1) / BN;
     const int band = tile_band(TC_BM, K);
+    const bool grouped = group.offsets != nullptr;
     const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
     const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
 
@@ -520,7 +552,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                                   // A is the previous kernel's output
+    pdl_wait();                                   // A (and the groups' offsets) are earlier kernels' output
+    const int m_tiles = grouped ? group_row_tiles(group) : (M + TC_BM - 1) / TC_BM;
+    const int total_tiles = m_tiles * n_tiles;
 
     // A block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ...; neighbouring tiles share their
     // W rows (m runs fastest), so blocks that run together read the same W tile from L2.
@@ -529,9 +563,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         int it = 0;                               // k iterations issued so far, over all tiles
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            int m_tile, n_tile;
-            tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
-            const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
+            int m_tile, n_tile, m0, w0;
+            if (grouped) {
+                int m_end, owner;
+                n_tile = tile / m_tiles;
+                group_tile(group, tile - n_tile * m_tiles, m0, m_end, owner);
+                w0 = owner * N + n_tile * BN;     // the group's own matrix among the stacked ones
+            } else {
+                tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
+                m0 = m_tile * TC_BM;
+                w0 = n_tile * BN;
+            }
             for (int i = 0; i < k_iters; ++i, ++it) {
                 const int s = it % STAGES;
                 if (it >= STAGES) ok = mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, flag);
@@ -540,7 +582,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t a_dst = smem_addr(tiles + (size_t)s * STAGE_BYTES);
                     mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, i * TC_BK, m0, full0 + 8 * s);
-                    tma_load_2d(a_dst + A_BYTES, &map_w, i * TC_BK, n0, full0 + 8 * s);
+                    tma_load_2d(a_dst + A_BYTES, &map_w, i * TC_BK, w0, full0 + 8 * s);
                 }
                 __syncwarp();
             }
@@ -593,16 +635,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             ok = mbar_wait(acc_full0 + 8 * buf, (local >> 1) & 1, flag);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            int m_tile, n_tile;
-            tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
-            const int m0 = m_tile * TC_BM, n0 = n_tile * BN;
+            int m_tile, n_tile, m0, rows_end = M;
+            if (grouped) {
+                int owner;
+                n_tile = tile / m_tiles;
+                group_tile(group, tile - n_tile * m_tiles, m0, rows_end, owner);
+            } else {
+                tile_coordinates(tile, m_tiles, n_tiles, band, m_tile, n_tile);
+                m0 = m_tile * TC_BM;
+            }
+            const int n0 = n_tile * BN;
             if (mode == TC_MODE_QKV_ROPE) {
                 if constexpr (BN % 128 == 0)
                     epilogue_tile_rope<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, rope,
                                            M, N, m0, n0);
             } else {
                 epilogue_tile<BN>(tmem_base + (uint32_t)buf * ACC_STRIDE, quarter, lane, slabs, buffer, &map_out, tma_out, out,
-                                  M, N, mode, act, m0, n0);
+                                  rows_end, N, mode, act, m0, n0);
             }
             // the accumulator has been read out: hand it back to the issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1176,7 +1225,38 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
     const long long tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
     dim3 grid((unsigned)(tiles < sm_count ? tiles : sm_count));     // one persistent block per SM at most
     return launch_pdl("skv_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
-                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, act, flag, rope);
+                      map_a, map_w, map_out, tma_out, out, M, N, K, mode, act, flag, rope, GroupArgs{nullptr, 0});
+}
+
+// The grouped form of the kernel above: `a` [rows, K] sorted by group, `w` [groups, N, K], `out` [rows, N] (bfloat16
+// with the activation, or float).  The threads store their rows themselves (a tile's rows past its group are another
+// group's).  Blocks beyond the tiles there turn out to be leave at once.
+int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
+                           int groups, int N, int K, act_t act, int* flag, cudaStream_t stream) {
+    constexpr int BN = 128, STAGES = 4;
+    if (K % 8 != 0) return fail("skv_expert_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
+    if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_expert_linear(tcgen05)", "operands must be 16-byte aligned");
+    if ((long long)groups * N > 0x7fffffffLL) return fail("skv_expert_linear(tcgen05)", "too many weight rows");
+    CUtensorMap map_a, map_w;
+    if (int code = tensor_map(a, rows, K, 2, TC_BM, TC_BK, &map_a)) return code;
+    if (int code = tensor_map(w, groups * N, K, 2, BN, TC_BK, &map_w)) return code;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 4 * 2 * 4096 +
+                            (2 * STAGES + 4) * 8 + 16 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t status = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>,
+                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("skv_expert_linear(tcgen05)", cudaGetErrorString(status));
+        configured = true;
+    }
+    const int sms = tc_sm_count();
+    if (sms <= 0) return fail("skv_expert_linear(tcgen05)", "cannot read the number of SMs");
+    // no group leaves more than one part tile
+    const long long tiles = ((long long)(rows + TC_BM - 1) / TC_BM + groups) * ((N + BN - 1) / BN);
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+    const int mode = out_is_float ? TC_MODE_STORE_F32 : TC_MODE_STORE;
+    return launch_pdl("skv_expert_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
+                      map_a, map_w, map_a, 0, out, rows, N, K, mode, act, flag, RopeArgs{}, GroupArgs{offsets, groups});
 }
 
 // The two-block form: clusters of two blocks, as many as the GPU runs at once (74 on 148 SMs), walk the 256 x 256 tiles.

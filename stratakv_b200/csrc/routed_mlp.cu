@@ -234,6 +234,22 @@ expert_linear_kernel(const TIn* __restrict__ a, int a_stride, const int* __restr
     }
 }
 
+// ---- rows in sorted order --------------------------------------------------------------------------------------------
+// out[p] = a[rows[p]] for every sorted pair p: the tensor-core projection reads whole tiles of neighbouring rows.
+// Rows are K numbers, K * sizeof(T) a multiple of 16 bytes; a warp copies a row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const T* __restrict__ a, int a_stride, const int* __restrict__ rows, T* __restrict__ out, int pairs, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (p >= pairs) return;
+    const uint4* src = (const uint4*)(a + (size_t)rows[p] * a_stride);
+    uint4* dst = (uint4*)(out + (size_t)p * K);
+    const int pieces = K * (int)sizeof(T) / 16;
+    for (int i = lane; i < pieces; i += 32) dst[i] = src[i];
+}
+
 // ---- the weighted sum ----------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 combine_experts_kernel(const float* __restrict__ results, const int* __restrict__ place, const float* __restrict__ weights,
@@ -258,6 +274,12 @@ combine_experts_kernel(const float* __restrict__ results, const int* __restrict_
         x[at] = add ? x[at] + total : total;
     }
 }
+
+#if SKV_DTYPE == SKV_BF16
+// gemm_tcgen05.cu: the tensor-memory GEMM over rows sorted by group
+int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
+                           int groups, int N, int K, act_t act, int* flag, cudaStream_t stream);
+#endif
 
 }  // namespace skv
 
@@ -295,14 +317,21 @@ SKV_EXPORT int skv_sort_by_expert(const int* chosen, int pairs, int top, int exp
 
 // a [a_rows, a_stride] and w [experts, N, K] in the compute dtype; rows int [pairs] or null (row p reads a[p]);
 // out [pairs, N] float (out_is_float) or the compute dtype; act: an activation's code or -1 for none.
+// In bfloat16, rows that lie in sorted order already (rows null, a_stride = K) with K a multiple of 8 go to the
+// tensor-memory GEMM's grouped form; `flag` is where its bounded waits report that they gave up.
 SKV_EXPORT int skv_expert_linear(const void* a, int a_stride, int a_rows, const int* rows, const void* w,
                                  const int* offsets, void* out, int out_is_float, int pairs, int experts, int N, int K,
-                                 int act, cudaStream_t stream) {
+                                 int act, int* flag, cudaStream_t stream) {
     if (pairs <= 0) return 0;
     if (experts <= 0 || experts > ROUTE_MAX_EXPERTS || N <= 0 || K <= 0 || a_stride < K || a_rows <= 0)
         return fail("skv_expert_linear", "sizes do not agree");
     if (!a || !w || !offsets || !out) return fail("skv_expert_linear", "rows, weights, offsets and a place for the result are needed");
     if (act >= ACT_SWIGLU_CLAMP) return fail("skv_expert_linear", "this activation is not served");
+#if SKV_DTYPE == SKV_BF16
+    if (!rows && a_stride == K && K % 8 == 0 && a_rows >= pairs && !(((uintptr_t)a | (uintptr_t)w) & 15))
+        return grouped_linear_tcgen05(a, w, offsets, out, out_is_float, pairs, experts, N, K,
+                                      act >= 0 ? ((act_t)act | ACT_ON_STORE) : (act_t)0, flag, stream);
+#endif
     const int row_tiles = (pairs + EXP_ROWS - 1) / EXP_ROWS + experts;       // no expert leaves more than one part tile
     if (row_tiles > 65535) return fail("skv_expert_linear", "too many rows for one launch");
     const dim3 grid((N + EXP_OUTS - 1) / EXP_OUTS, row_tiles);
@@ -311,6 +340,17 @@ SKV_EXPORT int skv_expert_linear(const void* a, int a_stride, int a_rows, const 
                           (const skv_t*)a, a_stride, rows, (const skv_t*)w, offsets, (float*)out, experts, N, K, act);
     return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, skv_t>, grid, dim3(256), 0, stream,
                       (const skv_t*)a, a_stride, rows, (const skv_t*)w, offsets, (skv_t*)out, experts, N, K, act);
+}
+
+// out [pairs, K] = a[rows[p]] (compute dtype; K * element size a multiple of 16 bytes, both 16-byte aligned).
+SKV_EXPORT int skv_gather_rows(const void* a, int a_stride, const int* rows, void* out, int pairs, int K,
+                               cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (!a || !rows || !out || K <= 0 || a_stride < K) return fail("skv_gather_rows", "rows, their indices and a place for them are needed");
+    if ((K * sizeof(skv_t)) % 16 || (a_stride * sizeof(skv_t)) % 16 || (((uintptr_t)a | (uintptr_t)out) & 15))
+        return fail("skv_gather_rows", "rows must be whole 16-byte pieces");
+    return launch_pdl("skv_gather_rows", gather_rows_kernel<skv_t>, dim3((pairs + 7) / 8), dim3(256), 0, stream,
+                      (const skv_t*)a, a_stride, rows, (skv_t*)out, pairs, K);
 }
 
 SKV_EXPORT int skv_combine_experts(const float* results, const int* place, const float* weights, const float* shared,

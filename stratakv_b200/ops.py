@@ -870,7 +870,20 @@ class Kernels:
         self._check(self.lib.skv_sort_by_expert(_ptr(chosen), n * top, int(top), int(experts), _ptr(offsets), _ptr(order),
                                                 _ptr(place), _stream()), "sort_by_expert")
 
-    def expert_linear(self, a, w, offsets, out, rows=None, activation: Optional[str] = None):
+    def gather_rows(self, a, rows, out):
+        """``out[p] = a[rows[p]]`` (compute dtype, rows of whole 16 bytes)."""
+        self._want(a, self.dtype, "a"); self._want(out, self.dtype, "out"); self._want(rows, torch.int32, "rows")
+        if out.shape[0] != rows.numel() or out.shape[1] != a.shape[1]:
+            raise KernelError("gather_rows: shapes do not agree")
+        self._check(self.lib.skv_gather_rows(_ptr(a), a.stride(0), _ptr(rows), _ptr(out), out.shape[0], out.shape[1],
+                                             _stream()), "gather_rows")
+
+    def expert_rows_sorted_first(self, hidden: int) -> bool:
+        """True if ``expert_linear`` is faster on rows that lie in sorted order (``gather_rows`` first): the bfloat16
+        build's tensor-core form wants neighbouring rows of whole 16 bytes."""
+        return self.dtype == torch.bfloat16 and hidden % 8 == 0
+
+    def expert_linear(self, a, w, offsets, out, rows=None, activation: Optional[str] = None, flag=None):
         """``out[p] = act(w[e] . a[row(p)])`` for every sorted pair p of expert e (``offsets`` from ``sort_by_expert``);
         ``w`` ``[experts, N, K]``; ``row(p) = rows[p]`` (the first projection gathers its input from the tokens) or p.
         ``out`` ``[pairs, N]`` is the compute dtype (with ``activation``) or float32.  Sums are float32."""
@@ -890,7 +903,7 @@ class Kernels:
         self._check(self.lib.skv_expert_linear(
             _ptr(a), a.stride(0), a.shape[0], _ptr(rows), _ptr(w), _ptr(offsets), _ptr(out),
             int(out.dtype == torch.float32), pairs, experts, N, K, ACTIVATIONS[activation] if activation is not None else -1,
-            _stream()), "expert_linear")
+            _ptr(flag if flag is not None else self.error_flag), _stream()), "expert_linear")
 
     def combine_experts(self, results, place, weights, shared, share, x, add: bool = True):
         """``x[t] (+)= sum_k weights[t, k] * results[place[t, k]] + share[t] * shared[t]`` (float32; ``shared`` may be

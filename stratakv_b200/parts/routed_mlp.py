@@ -102,7 +102,13 @@ class RoutedMlp(FeedForward):
         place = get("routed_place", (n, s.top), torch.int32)         # where each (token, choice) went
         ops.sort_by_expert(chosen, s.experts, offsets, order, place)
         hidden = get("routed_hidden", (pairs, self.padded), rt.dtype)
-        ops.expert_linear(h, self.w_up, offsets, hidden, rows=order, activation=s.activation)
+        if ops.expert_rows_sorted_first(s.hidden_size):
+            # the tensor-core projection reads tiles of neighbouring rows: bring the tokens' rows into sorted order first
+            gathered = get("routed_rows", (pairs, s.hidden_size), rt.dtype)
+            ops.gather_rows(h, order, gathered)
+            ops.expert_linear(gathered, self.w_up, offsets, hidden, activation=s.activation)
+        else:
+            ops.expert_linear(h, self.w_up, offsets, hidden, rows=order, activation=s.activation)
         results = get("routed_results", (pairs, s.hidden_size), torch.float32)
         ops.expert_linear(hidden, self.w_down, offsets, results)
         shared_out = None

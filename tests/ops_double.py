@@ -311,7 +311,10 @@ class DoubleKernels:
         order.copy_((sorted_pairs // chosen.shape[1]).to(torch.int32))
         place.view(-1)[sorted_pairs] = torch.arange(flat.numel(), dtype=torch.int32)
 
-    def expert_linear(self, a, w, offsets, out, rows=None, activation=None):
+    def expert_rows_sorted_first(self, hidden):
+        return False
+
+    def expert_linear(self, a, w, offsets, out, rows=None, activation=None, flag=None):
         self.calls.append("expert_linear")
         for e in range(w.shape[0]):
             lo, hi = int(offsets[e]), int(offsets[e + 1])

@@ -337,6 +337,14 @@ def test_experts_over_sorted_pairs_and_their_weighted_sum(dtype, shape):
         assert int(offsets[flat_expert[pair]]) <= at < int(offsets[flat_expert[pair] + 1]) and int(order[at]) == pair // top
     hidden_rows = torch.empty(n * top, ff, dtype=dtype, device="cuda")
     ops.expert_linear(h.to(dtype).cuda(), up.to(dtype).cuda(), offsets, hidden_rows, rows=order, activation="relu2")
+    if ops.expert_rows_sorted_first(hidden):                      # the other way: rows brought into sorted order first
+        gathered = torch.empty(n * top, hidden, dtype=dtype, device="cuda")
+        ops.gather_rows(h.to(dtype).cuda(), order, gathered)
+        assert torch.equal(gathered.cpu(), h.to(dtype)[order.cpu().long()])
+        other = torch.full_like(hidden_rows, 5.0)
+        ops.expert_linear(gathered, up.to(dtype).cuda(), offsets, other, activation="relu2")
+        close(other, hidden_rows.double().cpu(), dtype, "hidden rows from sorted rows", loose=2.0)
+        hidden_rows = other
     results = torch.empty(n * top, hidden, device="cuda")
     ops.expert_linear(hidden_rows, down.to(dtype).cuda(), offsets, results)
     shared_out = None
