@@ -248,8 +248,8 @@ def povusun_arm(args) -> int:
 def kedelorn_config(size, layers, vocab, kinds, streams=2):
     """A Kedelorn configuration at a size of DESIGN_SIZES whose layer i has the mixer ``kinds[i % len(kinds)]``.  The
     retention layers have Llama's heads with keys and values of the head size, the whole head rotated, and decays
-    from 1 - 2^-5 to 1 - 2^-8.  The latent layers have Llama's heads, an unrotated part of the head size and a rotated
-    one of half of it with stretched frequencies, a latent of four heads' width (at most 256) as the Povusun arm has,
+    from 1 - 2^-5 to 1 - 2^-8.  The latent layers have Llama's heads and head size, of which a quarter is the rotated
+    part with stretched frequencies, values of the head size, a latent of four heads' width (at most 256) as the Povusun arm has,
     a sink and a gate; where the mix has latent layers, every second of them attends over the one before.  The
     feed-forward has eight experts of which two, and a shared one, each half as wide as Llama's: a token passes
     through as many feed-forward weights as in Llama (two matrices an expert, three there)."""
@@ -264,8 +264,8 @@ def kedelorn_config(size, layers, vocab, kinds, streams=2):
             mixer = {"heads": heads, "dim": d, "vdim": d, "rot": {"dims": d, "base": 10000.0},
                      "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(heads - 1, 1)) for h in range(heads)]}
         else:
-            mixer = {"heads": heads, "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": min(256, 4 * d), "scale": (1.5 * d) ** -0.5,
-                     "rot": {"dims": d // 2, "base": 10000.0,
+            mixer = {"heads": heads, "dim": d - d // 4, "rot_dim": d // 4, "vdim": d, "kv_rank": min(256, 4 * d), "scale": d ** -0.5,
+                     "rot": {"dims": d // 4, "base": 10000.0,
                              "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
             if len(latents) % 2 == 1:
                 mixer["kv_from"] = latents[-1]

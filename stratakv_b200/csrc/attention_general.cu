@@ -213,13 +213,18 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                          int num_kv_heads, int dim, int vdim, int block_size, float scale, int window,
                          const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ gate,
                          int gate_stride, int out_stride, float softcap, int gate_per_element,
-                         const float* __restrict__ sink, int v_stride) {
+                         const float* __restrict__ sink, int v_stride, int splits, float* __restrict__ partial_o,
+                         float* __restrict__ partial_ml) {
     extern __shared__ __align__(16) float general_q[];          // [GEN_WARPS][dim rounded up to 4]
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * GEN_WARPS + warp;
-    if (item >= (long long)n_tokens * num_heads) return;        // whole warps leave together
+    const long long work = (long long)blockIdx.x * GEN_WARPS + warp;
+    if (work >= (long long)n_tokens * num_heads * splits) return;        // whole warps leave together
+    // With splits > 1 a warp takes one part of its (token, head)'s keys and leaves its sums, their maximum and its
+    // unnormalised output for attention_general_merge_kernel; the heads of a token stay side by side in a block.
+    const long long item = splits > 1 ? (work / ((long long)num_heads * splits)) * num_heads + work % num_heads : work;
+    const int split = splits > 1 ? (int)((work / num_heads) % splits) : 0;
     const int t = (int)(item / num_heads), head = (int)(item % num_heads);
     const int kv_head = head / (num_heads / num_kv_heads);
     const int pos = positions[t];
@@ -237,9 +242,16 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     for (int i = 0; i < GEN_ACC; ++i) acc[i] = 0.0f;
     float running_max = -INFINITY, running_sum = 0.0f;
 
-    for (int j0 = lo; j0 <= pos; j0 += 32) {
+    // this warp's keys: all of lo .. pos, or its part of them in whole runs of 32
+    int first_key = lo, last_key = pos;
+    if (splits > 1) {
+        const int runs = (pos - lo + 32) / 32, per_split = (runs + splits - 1) / splits;
+        first_key = lo + split * per_split * 32;
+        last_key = min(pos, first_key + per_split * 32 - 1);
+    }
+    for (int j0 = first_key; j0 <= last_key; j0 += 32) {
         const int j = j0 + lane;
-        const bool valid = j <= pos;
+        const bool valid = j <= last_key;
         size_t row = 0;                                // row of this key in units of one head's vector
         float score = -INFINITY;
         if (valid) {
@@ -256,7 +268,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         running_max = new_max;
 #pragma unroll
         for (int i = 0; i < GEN_ACC; ++i) acc[i] *= rescale;
-        const int count = min(32, pos - j0 + 1);
+        const int count = min(32, last_key - j0 + 1);
         for (int jj = 0; jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, jj);
@@ -267,6 +279,19 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
                 if (d < vdim) acc[i] = fmaf(pj, to_float(v_row[d]), acc[i]);
             }
         }
+    }
+    if (splits > 1) {
+        float* o_part = partial_o + ((size_t)item * splits + split) * vdim;
+#pragma unroll
+        for (int i = 0; i < GEN_ACC; ++i) {
+            const int d = lane + 32 * i;
+            if (d < vdim) o_part[d] = acc[i];
+        }
+        if (lane == 0) {
+            partial_ml[((size_t)item * splits + split) * 2] = running_max;      // -infinity: this part had no keys
+            partial_ml[((size_t)item * splits + split) * 2 + 1] = running_sum;
+        }
+        return;
     }
     // a sink counts once in the denominator: it has no key and no value, and is not scaled
     if (sink) running_sum += expf(sink[head] - running_max);
@@ -284,6 +309,44 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
         }
     }
     // columns that pad a row for the projection after it are zero
+    if (head == num_heads - 1)
+        for (int c = num_heads * vdim + lane; c < out_stride; c += 32) out[(size_t)t * out_stride + c] = from_float<T>(0.0f);
+}
+
+// The parts of a (token, head) that attention_general_kernel left with splits > 1, put together: the largest maximum,
+// the sums and outputs brought to it, the sink, the gate.  A warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(GEN_WARPS * 32)
+attention_general_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                               T* __restrict__ out, int n_tokens, int num_heads, int vdim, int splits,
+                               const float* __restrict__ gate, int gate_stride, int out_stride, int gate_per_element,
+                               const float* __restrict__ sink) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * GEN_WARPS + warp;
+    if (item >= (long long)n_tokens * num_heads) return;
+    const int t = (int)(item / num_heads), head = (int)(item % num_heads);
+    const float* ml = partial_ml + (size_t)item * splits * 2;
+    float top = -INFINITY;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, ml[2 * s]);      // (the first part always has the first key)
+    float total = 0.0f;
+    for (int s = 0; s < splits; ++s) total += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * expf(ml[2 * s] - top);
+    if (sink) total += expf(sink[head] - top);
+    float factor = 1.0f / total;
+    if (gate && !gate_per_element) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + head]));
+    const float* gate_row = gate && gate_per_element ? gate + (size_t)t * gate_stride + (size_t)head * vdim : nullptr;
+    T* out_row = out + (size_t)t * out_stride + (size_t)head * vdim;
+    for (int d = lane; d < vdim; d += 32) {
+        float value = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            if (ml[2 * s] == -INFINITY) continue;
+            value = fmaf(partial_o[((size_t)item * splits + s) * vdim + d], expf(ml[2 * s] - top), value);
+        }
+        value *= factor;
+        if (gate_row) value *= 1.0f / (1.0f + expf(-gate_row[d]));
+        out_row[d] = from_float<T>(value);
+    }
     if (head == num_heads - 1)
         for (int c = num_heads * vdim + lane; c < out_stride; c += 32) out[(size_t)t * out_stride + c] = from_float<T>(0.0f);
 }
@@ -341,8 +404,11 @@ SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const v
                                      int n_tokens, int num_heads, int num_kv_heads, int dim, int vdim, int block_size,
                                      float scale, int window, const float* r1, const float* r2, const float* gate,
                                      int gate_stride, int out_stride, float softcap, int gate_per_element,
-                                     const float* sink, int value_stride, cudaStream_t stream) {
+                                     const float* sink, int value_stride, int splits, float* partial_o,
+                                     float* partial_ml, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (splits < 1 || splits > 1024 || (splits > 1 && (!partial_o || !partial_ml)))
+        return fail("skv_attention_general", "1 to 1024 parts of the keys, and with more than one the scratch for them");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_general", "heads must be a positive multiple of kv heads");
     if (dim <= 0 || vdim <= 0 || vdim > GEN_MAX_VDIM) return fail("skv_attention_general", "value heads of 1 to 512 numbers are served");
@@ -355,12 +421,18 @@ SKV_EXPORT int skv_attention_general(const void* q, const void* k_cache, const v
     const size_t smem = (size_t)GEN_WARPS * ((dim + 3) & ~3) * sizeof(float);
     if (smem > 48 * 1024) return fail("skv_attention_general", "the key size is too large");
     const long long items = (long long)n_tokens * num_heads;
-    const long long blocks = (items + GEN_WARPS - 1) / GEN_WARPS;
+    const long long blocks = (items * splits + GEN_WARPS - 1) / GEN_WARPS;
     if (blocks > 0x7fffffffLL) return fail("skv_attention_general", "too many tokens in one step");
     auto kernel = vdim <= 256 ? attention_general_kernel<skv_t, 8> : attention_general_kernel<skv_t, 16>;
-    return launch_pdl("skv_attention_general", kernel, dim3((unsigned)blocks),
-                      dim3(GEN_WARPS * 32), smem, stream, (const skv_t*)q, (const skv_t*)k_cache,
-                      (const skv_t*)v_cache, block_table, table_width, positions, token_seq, (skv_t*)out, n_tokens,
-                      num_heads, num_kv_heads, dim, vdim, block_size, scale, window, r1, r2, gate, gate_stride, out_stride,
-                      softcap, gate_per_element, sink, value_stride);
+    if (int code = launch_pdl("skv_attention_general", kernel, dim3((unsigned)blocks),
+                              dim3(GEN_WARPS * 32), smem, stream, (const skv_t*)q, (const skv_t*)k_cache,
+                              (const skv_t*)v_cache, block_table, table_width, positions, token_seq, (skv_t*)out, n_tokens,
+                              num_heads, num_kv_heads, dim, vdim, block_size, scale, window, r1, r2, gate, gate_stride,
+                              out_stride, softcap, gate_per_element, sink, value_stride, splits, partial_o, partial_ml))
+        return code;
+    if (splits == 1) return 0;
+    return launch_pdl("skv_attention_general(merge)", attention_general_merge_kernel<skv_t>,
+                      dim3((unsigned)((items + GEN_WARPS - 1) / GEN_WARPS)), dim3(GEN_WARPS * 32), 0, stream,
+                      (const float*)partial_o, (const float*)partial_ml, (skv_t*)out, n_tokens, num_heads, vdim, splits,
+                      gate, gate_stride, out_stride, gate_per_element, sink);
 }

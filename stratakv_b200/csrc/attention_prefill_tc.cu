@@ -430,7 +430,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && n_tiles > 0) ok = a_wait(bar(B_PE, (n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, flag);
         if (ok && n_tiles > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inverse = (EXTRAS ? gate_factor(extras, q_begin + min(q_row, q_len - 1), head) : 1.0f) / row_sum;
+            // (a sink has no key and no value and is not scaled; the sums are in units of log2 below used_max)
+            const float sunk = EXTRAS && extras.sink ? a_exp2(fmaf(extras.sink[head], 1.4426950408889634f, -used_max)) : 0.0f;
+            const float inverse = (EXTRAS ? gate_factor(extras, q_begin + min(q_row, q_len - 1), head) : 1.0f) / (row_sum + sunk);
             __nv_bfloat16* dst = out + ((size_t)(q_begin + min(q_row, q_len - 1)) * num_heads + head) * AHD;
             const float* gate_row = EXTRAS && extras.gate && extras.gate_per_element
                 ? extras.gate + (size_t)(q_begin + min(q_row, q_len - 1)) * extras.gate_stride + (size_t)head * AHD : nullptr;
@@ -530,13 +532,13 @@ SKV_EXPORT int skv_attention_prefill_tc_extras(const void* q, const void* k_cach
                                                const int* ctx_after, void* out, int n_seqs, int n_tokens, int max_q_len,
                                                int num_heads, int num_kv_heads, int head_dim, int block_size, float scale,
                                                int window, const float* bias, int bias_len, const float* gate,
-                                               int gate_stride, float softcap, int gate_per_element, int* flag,
-                                               cudaStream_t stream) {
+                                               int gate_stride, float softcap, int gate_per_element, const float* sink,
+                                               int* flag, cudaStream_t stream) {
     if (n_seqs <= 0 || max_q_len <= 0) return 0;
     if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads * (gate_per_element ? head_dim : 1)) ||
         (gate_per_element && (!gate || gate_stride % 4 != 0 || ((uintptr_t)gate & 15))) || softcap < 0.0f)
         return fail("skv_attention_prefill_tc", "a bias table needs its length, a gate rows of at least heads numbers (with a gate per number: heads * head_dim, 16-byte aligned rows), a cap must not be negative");
-    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element};
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element, sink};
     if (head_dim != AHD) return fail("skv_attention_prefill_tc", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_prefill_tc", "heads must be a positive multiple of kv heads");
@@ -562,7 +564,7 @@ SKV_EXPORT int skv_attention_prefill_tc_extras(const void* q, const void* k_cach
         }
         configured = true;
     }
-    return launch_pdl("skv_attention_prefill_tc", bias || gate || softcap > 0.0f ? prefill_attention_tc_kernel<true> : prefill_attention_tc_kernel<false>,
+    return launch_pdl("skv_attention_prefill_tc", bias || gate || sink || softcap > 0.0f ? prefill_attention_tc_kernel<true> : prefill_attention_tc_kernel<false>,
                       dim3(num_heads, (unsigned)blocks),
                       dim3(ATHREADS), smem, stream, map_q, map_k, map_v, block_table, table_width, cu_q, ctx_after,
                       (__nv_bfloat16*)out, num_heads, num_kv_heads, block_size, rows_per_load, scale, window,
@@ -576,7 +578,7 @@ SKV_EXPORT int skv_attention_prefill_tc(const void* q, const void* k_cache, cons
                                         int window, int* flag, cudaStream_t stream) {
     return skv_attention_prefill_tc_extras(q, k_cache, v_cache, cache_blocks, block_table, table_width, cu_q, ctx_after,
                                            out, n_seqs, n_tokens, max_q_len, num_heads, num_kv_heads, head_dim, block_size,
-                                           scale, window, nullptr, 0, nullptr, 0, 0.0f, 0, flag, stream);
+                                           scale, window, nullptr, 0, nullptr, 0, 0.0f, 0, nullptr, flag, stream);
 }
 
 SKV_EXPORT int skv_has_attention_prefill_tc() { return 1; }
@@ -591,7 +593,8 @@ SKV_EXPORT int skv_attention_prefill_tc(const void*, const void*, const void*, i
 
 SKV_EXPORT int skv_attention_prefill_tc_extras(const void*, const void*, const void*, int, const int*, int, const int*,
                                                const int*, void*, int, int, int, int, int, int, int, float, int,
-                                               const float*, int, const float*, int, float, int, int*, cudaStream_t) {
+                                               const float*, int, const float*, int, float, int, const float*, int*,
+                                               cudaStream_t) {
     return skv::fail("skv_attention_prefill_tc", "this build (float32, or a head size other than 64 or 128) has no such kernel");
 }
 

@@ -164,6 +164,7 @@ struct AttentionExtras {
     int gate_stride;
     float softcap;
     int gate_per_element;
+    const float* sink;                 // [num_heads] or null: exp(sink[h]) counts once in the softmax's denominator
 };
 
 // tanh(x) = 1 - 2 / (1 + e^(2x)) with the special-function unit's exponential and reciprocal: an absolute error of a

@@ -344,8 +344,9 @@ class Kernels:
     def attention_prefill_tc(self, q, k_cache, v_cache, block_table, cu_q, ctx_after, out, max_q_len: int,
                              num_heads: int, num_kv_heads: int, head_dim: int, block_size: int, scale: float,
                              window: int = 0, flag=None, bias=None, gate=None, gate_stride: int = 0,
-                             softcap: float = 0.0, gate_per_element: bool = False):
+                             softcap: float = 0.0, gate_per_element: bool = False, sink=None):
         """``attention_prefill`` with both products on the tcgen05 tensor cores (bfloat16, head size 64 or 128).
+        ``sink`` (float32 per head): ``exp(sink[h])`` counts once in the softmax's denominator.
         ``softcap`` c > 0: scores become ``c * tanh(score / c)``; ``gate_per_element``: a logit for every output
         number, at ``[t * gate_stride + h * head_dim + d]``."""
         self._want(q, self.dtype, "q"); self._want(out, self.dtype, "out")
@@ -357,12 +358,16 @@ class Kernels:
             raise KernelError("attention_prefill_tc: one length, one offset pair and one table row per sequence is needed")
         if tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, head_dim) or k_cache.shape != v_cache.shape:
             raise KernelError("attention_prefill_tc: the cache must be [blocks, kv_heads, block_size, head_dim]")
+        if sink is not None:
+            self._want(sink, torch.float32, "sink")
+            if sink.numel() != num_heads:
+                raise KernelError("attention_prefill_tc: the sink must hold one number per head")
         self._check(self.lib.skv_attention_prefill_tc_extras(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(block_table), block_table.shape[1],
             _ptr(cu_q), _ptr(ctx_after), _ptr(out), n_seqs, q.shape[0], max_q_len, num_heads, num_kv_heads, head_dim,
             block_size, ctypes.c_float(scale), window,
             *self._extras(bias, gate, gate_stride, num_heads, "attention_prefill_tc", head_dim if gate_per_element else 0),
-            ctypes.c_float(softcap), int(bool(gate_per_element)),
+            ctypes.c_float(softcap), int(bool(gate_per_element)), _ptr(sink),
             _ptr(flag if flag is not None else self.error_flag), _stream()), "attention_prefill_tc")
 
     def attention_decode(self, q, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
@@ -525,8 +530,12 @@ class Kernels:
     def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads: int,
                           num_kv_heads: int, dim: int, vdim: int, block_size: int, scale: float, window: int = 0,
                           r1=None, r2=None, gate=None, gate_stride: int = 0, softcap: float = 0.0,
-                          gate_per_element: bool = False, sink=None, value_stride: int = 0):
-        """(``sink``, float32 per head: ``exp(sink[h])`` counts once in the softmax's denominator, with no value.
+                          gate_per_element: bool = False, sink=None, value_stride: int = 0, splits: int = 1,
+                          scratch_o=None, scratch_ml=None):
+        """(``splits`` > 1: every (token, head)'s keys are cut into that many parts that run side by side, for steps of
+        few tokens over long contexts; ``scratch_o`` float32 ``[tokens * heads * splits * vdim]`` and ``scratch_ml``
+        ``[tokens * heads * splits * 2]`` hold the parts for the merge that follows.)
+        (``sink``, float32 per head: ``exp(sink[h])`` counts once in the softmax's denominator, with no value.
         ``value_stride``: the values' rows are that many numbers apart where they are not ``vdim`` wide, so that the
         first ``vdim`` numbers of the cached keys can serve as the values.)
         (``softcap`` c > 0: scores become ``c * tanh(score / c)``.  ``gate_per_element``: the gate holds a logit for
@@ -557,11 +566,17 @@ class Kernels:
         n = q.shape[0]
         if tuple(q.shape) != (n, num_heads * dim) or out.shape[0] != n or out.shape[1] < num_heads * vdim:
             raise KernelError("attention_general: q must be [tokens, heads * dim] and out [tokens, heads * vdim or wider]")
+        if splits > 1:
+            self._want(scratch_o, torch.float32, "scratch_o"); self._want(scratch_ml, torch.float32, "scratch_ml")
+            if scratch_o.numel() < n * num_heads * splits * vdim or scratch_ml.numel() < n * num_heads * splits * 2:
+                raise KernelError("attention_general: the scratch for the parts is too small")
         self._check(self.lib.skv_attention_general(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(positions),
             _ptr(token_seq), _ptr(out), n, num_heads, num_kv_heads, dim, vdim, block_size, ctypes.c_float(scale),
             window, _ptr(r1), _ptr(r2), _ptr(gate), gate_stride, out.shape[1], ctypes.c_float(softcap),
-            int(bool(gate_per_element)), _ptr(sink), int(value_stride), _stream()), "attention_general")
+            int(bool(gate_per_element)), _ptr(sink), int(value_stride), int(splits),
+            _ptr(scratch_o if splits > 1 else None), _ptr(scratch_ml if splits > 1 else None), _stream()),
+            "attention_general")
 
     def paged_gather(self, cache, block_table, positions, seqs, out):
         """``out[i, :]`` = the row that a one-head paged cache (``[blocks, 1, block_size, width]``) holds for position
@@ -798,20 +813,28 @@ class Kernels:
     # ---- latent attention with a rotated part ---------------------------------------------
     def latent_finish(self, fused, q_plain, q_folded, cache, positions, token_seq, block_table, heads: int, dim: int,
                       rope_dim: int, latent_dim: int, block_size: int, rotation=None, rotated: int = 0,
-                      latent_offset: int = 0, latent_gamma=None, eps: float = 0.0, write_cache: bool = True):
+                      latent_offset: int = 0, latent_gamma=None, eps: float = 0.0, write_cache: bool = True,
+                      q_whole=None):
         """From float32 rows of a fused projection ``[queries: heads x (dim | rope_dim) | latent_dim + rope_dim | ...]``:
         the unrotated query parts to ``q_plain`` ``[tokens, heads * dim]``, the rotated ones (first ``rotated`` numbers
         turned by ``rotation`` ``[positions, rotated / 2, 2]``) to the last ``rope_dim`` columns of every head of
         ``q_folded`` ``[tokens, heads * (latent_dim + rope_dim)]``; with ``write_cache`` the latent, divided by its root
         mean square and times ``latent_gamma``, and the rotated key part behind it go to the token's row of ``cache``
-        ``[blocks, 1, block_size, latent_dim + rope_dim]``."""
-        self._want(fused, torch.float32, "fused"); self._want(q_plain, self.dtype, "q_plain")
-        self._want(q_folded, self.dtype, "q_folded"); self._want(cache, self.dtype, "cache")
+        ``[blocks, 1, block_size, latent_dim + rope_dim]``.  With ``q_whole`` ``[tokens, heads * (dim + rope_dim)]`` both
+        query parts go there instead, head by head, and ``q_plain`` and ``q_folded`` may be None."""
+        self._want(fused, torch.float32, "fused"); self._want(cache, self.dtype, "cache")
+        n, key_dim = fused.shape[0], latent_dim + rope_dim
+        if q_whole is not None:
+            self._want(q_whole, self.dtype, "q_whole")
+            if tuple(q_whole.shape) != (n, heads * (dim + rope_dim)):
+                raise KernelError("latent_finish: q_whole must be [tokens, heads * (dim + rope_dim)]")
+        else:
+            self._want(q_plain, self.dtype, "q_plain"); self._want(q_folded, self.dtype, "q_folded")
+            if tuple(q_plain.shape) != (n, heads * dim) or tuple(q_folded.shape) != (n, heads * key_dim):
+                raise KernelError("latent_finish: shapes do not agree")
         self._want(positions, torch.int32, "positions"); self._want(token_seq, torch.int32, "token_seq")
         self._want(block_table, torch.int32, "block_table")
-        n, key_dim = fused.shape[0], latent_dim + rope_dim
-        if (tuple(q_plain.shape) != (n, heads * dim) or tuple(q_folded.shape) != (n, heads * key_dim)
-                or tuple(cache.shape[1:]) != (1, block_size, key_dim) or positions.numel() != n or token_seq.numel() != n):
+        if (tuple(cache.shape[1:]) != (1, block_size, key_dim) or positions.numel() != n or token_seq.numel() != n):
             raise KernelError("latent_finish: shapes do not agree")
         if fused.shape[1] < heads * (dim + rope_dim) + (key_dim if write_cache else 0) or (write_cache and latent_offset < heads * (dim + rope_dim)):
             raise KernelError("latent_finish: a row is shorter than its queries, latent and key part")
@@ -824,7 +847,7 @@ class Kernels:
             if latent_gamma.numel() != latent_dim:
                 raise KernelError("latent_finish: the latent's norm weight must hold latent_dim numbers")
         self._check(self.lib.skv_latent_finish(
-            _ptr(fused), fused.shape[1], _ptr(q_plain), _ptr(q_folded), _ptr(cache), _ptr(positions), _ptr(token_seq),
+            _ptr(fused), fused.shape[1], _ptr(q_plain), _ptr(q_folded), _ptr(q_whole), _ptr(cache), _ptr(positions), _ptr(token_seq),
             _ptr(block_table), block_table.shape[1], n, heads, dim, rope_dim, latent_dim, block_size, _ptr(rotation),
             int(rotated if rotation is not None else 0), rotation.shape[0] if rotation is not None else 0,
             int(latent_offset), _ptr(latent_gamma), ctypes.c_float(eps), int(bool(write_cache)), _stream()), "latent_finish")

@@ -110,6 +110,19 @@ class LatentAttention(Mixer):
         # keys' and values' up-projections as one matrix, for steps that make every head's keys and values
         self.w_kv_up = (torch.cat([self.rt.upload(tensors[s.k_up_weight]), self.rt.upload(tensors[s.v_up_weight])],
                                   dim=0).contiguous() if not self.extended else None)
+        # the same for a layer with a rotated part: a cached row is [latent | rotated key part], and rows of the
+        # identity copy the rotated part behind every head's unrotated keys (exactly: one product a number)
+        self.w_kv_whole = None
+        if (self.extended and self.rt.dtype == torch.bfloat16 and self.q_head == s.v_head_dim and self.q_head in (64, 128)
+                and self.key_dim % 8 == 0):
+            k_up = self.rt.upload(tensors[s.k_up_weight]).view(s.num_heads, s.head_dim, s.latent_dim)
+            keys = k_up.new_zeros(s.num_heads, self.q_head, self.key_dim)
+            keys[:, :s.head_dim, :s.latent_dim] = k_up
+            if self.rope_dim:
+                keys[:, s.head_dim:, s.latent_dim:] = torch.eye(self.rope_dim, dtype=k_up.dtype, device=k_up.device)
+            values = k_up.new_zeros(s.num_heads * s.v_head_dim, self.key_dim)
+            values[:, :s.latent_dim] = self.rt.upload(tensors[s.v_up_weight])
+            self.w_kv_whole = torch.cat([keys.view(s.num_heads * self.q_head, self.key_dim), values], dim=0).contiguous()
         w_o = self.rt.upload(tensors[s.o_weight])
         if self.ctx_width != self.ctx_dim:
             w_o = torch.cat([w_o, w_o.new_zeros(s.hidden_size, self.ctx_width - self.ctx_dim)], dim=1)
@@ -126,7 +139,7 @@ class LatentAttention(Mixer):
         table = step.block_tables[group]
         block_size = step.cache.block_size
         if self.extended:
-            self._forward_extended(step, fused, latents, table, writes_cache)
+            self._forward_extended(step, fused, latents, table, writes_cache, group)
             ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
             ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
             return
@@ -140,16 +153,30 @@ class LatentAttention(Mixer):
             self._attend_folded(step, q, ctx, latents, table)
         ops.linear(ctx, self.w_o, x, _residual_mode(step), stats=_residual_stats(step))
 
-    def _forward_extended(self, step, fused, cached, table, writes_cache):
+    def _forward_extended(self, step, fused, cached, table, writes_cache, group):
         """The folded way with a rotated part, a sink and a gate: finish the projection's rows (the latent's norm, the
         rotations, the cache write), fold the keys' up-projection into the unrotated queries, attend with all heads
         over the cached rows, apply the values' up-projection."""
         s, rt = self.spec, self.rt
         ops = rt.kernels()
         n = fused.shape[0]
+        rotation = self.position.fusion_table(step.max_ctx) if self.position is not None else None
+        gate = fused[:, self.gate_offset:] if self.has_gate else None
+        if self.w_kv_whole is not None and self._expanded_serves(step, self.q_head):
+            # a prompt in bfloat16: whole query heads [unrotated | rotated] against every head's keys made from the
+            # cached rows; the sink and the gate are the tensor-core kernel's
+            q_whole = rt.workspace.get("q", (n, self.q_dim), rt.dtype)
+            ops.latent_finish(fused, None, None, cached, step.positions, step.token_seq, table, s.num_heads,
+                              s.head_dim, self.rope_dim, s.latent_dim, step.cache.block_size,
+                              rotation=rotation, rotated=s.rope.dims if rotation is not None else 0,
+                              latent_offset=self.q_dim, latent_gamma=self.latent_gamma, eps=s.eps,
+                              write_cache=writes_cache and not self.shares_kv, q_whole=q_whole)
+            ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
+            self._attend_expanded(step, q_whole, ctx, cached, table, group, head_dim=self.q_head, row_width=self.key_dim,
+                                  weight=self.w_kv_whole, gate=gate, gate_stride=self.fused_width, sink=self.sink)
+            return
         q_plain = rt.workspace.get("q", (n, s.num_heads * s.head_dim), rt.dtype)
         q_folded = rt.workspace.get("q_latent", (n, s.num_heads * self.key_dim), rt.dtype)
-        rotation = self.position.fusion_table(step.max_ctx) if self.position is not None else None
         ops.latent_finish(fused, q_plain, q_folded, cached, step.positions, step.token_seq, table, s.num_heads,
                           s.head_dim, self.rope_dim, s.latent_dim, step.cache.block_size,
                           rotation=rotation, rotated=s.rope.dims if rotation is not None else 0,
@@ -157,10 +184,19 @@ class LatentAttention(Mixer):
                           write_cache=writes_cache and not self.shares_kv)
         ops.headwise_linear(q_plain, self.w_k_up_t, q_folded, s.num_heads, out_head_stride=self.key_dim)
         mixed = rt.workspace.get("latent_ctx", (n, s.num_heads * s.latent_dim), rt.dtype)
+        # one token a sequence: few (token, head) pairs over long contexts, so each pair's keys are cut into parts that
+        # run side by side, enough to give every SM a few warps (a part is at least 64 keys)
+        splits, scratch_o, scratch_ml = 1, None, None
+        if step.is_decode and rt.device.type == "cuda":
+            splits = max(1, min(-(-rt.sm_count * 16 // (n * s.num_heads)), -(-step.max_ctx // 64), 64))
+            if splits > 1:
+                scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.latent_dim,), torch.float32)
+                scratch_ml = rt.workspace.get("attn_split_ml", (n * s.num_heads * splits * 2,), torch.float32)
         ops.attention_general(q_folded, cached, cached, table, step.positions, step.token_seq, mixed, s.num_heads, 1,
                               self.key_dim, s.latent_dim, step.cache.block_size, s.scale,
-                              gate=fused[:, self.gate_offset:] if self.has_gate else None, gate_stride=self.fused_width,
-                              sink=self.sink, value_stride=self.key_dim)
+                              gate=gate, gate_stride=self.fused_width,
+                              sink=self.sink, value_stride=self.key_dim, splits=splits, scratch_o=scratch_o,
+                              scratch_ml=scratch_ml)
         ctx = rt.workspace.get("attn_ctx", (n, self.ctx_width), rt.dtype)
         ops.headwise_linear(mixed, self.w_v_up, ctx, s.num_heads, zero_pad=self.ctx_width != self.ctx_dim)
 
@@ -197,20 +233,32 @@ class LatentAttention(Mixer):
                              step.cache.block_size, s.scale, 0, splits, scratch_o, scratch_ml)
         return True
 
-    def _attend_expanded(self, step, q, ctx, latents, table, group) -> bool:
-        """A prompt in bfloat16: every head's keys and values are made from the gathered cached vectors by one GEMM,
-        written as pages of a scratch cache, and the tensor-core prompt kernel attends over them as multi-head
-        attention.  False where that kernel does not serve (then the folded way does)."""
+    def _expanded_serves(self, step, head_dim) -> bool:
+        """True if this step can make every head's keys and values and attend on the tensor-core prompt kernel."""
         s, rt = self.spec, self.rt
         block_size = step.cache.block_size
-        if (step.is_decode or rt.dtype != torch.bfloat16 or rt.device.type != "cuda" or s.head_dim != s.v_head_dim
-                or s.head_dim not in (64, 128) or step.max_q_len <= 32 or block_size & (block_size - 1) or block_size < 16
+        if (step.is_decode or rt.dtype != torch.bfloat16 or rt.device.type != "cuda" or head_dim != s.v_head_dim
+                or head_dim not in (64, 128) or step.max_q_len <= 32 or block_size & (block_size - 1) or block_size < 16
                 or step.n_seqs * -(-step.max_q_len // 128) > 65535 or self.ctx_width != self.ctx_dim
                 or s.latent_dim % 8 != 0):          # (the up-projection GEMM reads rows of whole 16 bytes)
             return False
-        ops_d = rt.kernels(s.head_dim)
-        if not ops_d.has_attention_prefill_tc():
+        return rt.kernels(head_dim).has_attention_prefill_tc()
+
+    def _attend_expanded(self, step, q, ctx, latents, table, group, head_dim=None, row_width=None, weight=None,
+                         gate=None, gate_stride=0, sink=None) -> bool:
+        """A prompt in bfloat16: every head's keys and values are made from the gathered cached vectors by one GEMM,
+        written as pages of a scratch cache, and the tensor-core prompt kernel attends over them as multi-head
+        attention.  False where that kernel does not serve (then the folded way does).  ``head_dim``, ``row_width``
+        and ``weight``: the keys' size, the cached row's width and the matrix that makes ``[keys | values]`` of all
+        heads from a row (default: the plain latent's)."""
+        s, rt = self.spec, self.rt
+        block_size = step.cache.block_size
+        head_dim = head_dim or s.head_dim
+        row_width = row_width or s.latent_dim
+        weight = weight if weight is not None else self.w_kv_up
+        if not self._expanded_serves(step, head_dim):
             return False
+        ops_d = rt.kernels(head_dim)
         ops = rt.kernels()
         meta = step.scratch.get("expanded_context")
         if meta is None:
@@ -230,20 +278,21 @@ class LatentAttention(Mixer):
             meta = (total, base, device[:total], device[total:2 * total], device[2 * total:].view(step.n_seqs, width))
             step.scratch["expanded_context"] = meta
         total, pages, positions, seqs, scratch_table = meta
-        gathered = rt.workspace.get("latent_rows", (total, s.latent_dim), rt.dtype)
+        gathered = rt.workspace.get("latent_rows", (total, row_width), rt.dtype)
         ops.paged_gather(latents, table, positions, seqs, gathered)
-        kv_width = s.num_heads * (s.head_dim + s.v_head_dim)
+        kv_width = s.num_heads * (head_dim + s.v_head_dim)
         expanded = rt.workspace.get("latent_kv", (total, kv_width), torch.float32)
-        ops.linear(gathered, self.w_kv_up, expanded, _ops.MODE_STORE_F32)
-        keys = rt.workspace.get("latent_keys", (pages, s.num_heads, block_size, s.head_dim), rt.dtype)
+        ops.linear(gathered, weight, expanded, _ops.MODE_STORE_F32)
+        keys = rt.workspace.get("latent_keys", (pages, s.num_heads, block_size, head_dim), rt.dtype)
         values = rt.workspace.get("latent_values", (pages, s.num_heads, block_size, s.v_head_dim), rt.dtype)
         # (rows of a sequence's last page beyond its length are never seen, but a weight of zero times whatever the
         # scratch held, a NaN perhaps, is not zero)
         values.zero_()
-        ops.qkv_finish(expanded, None, keys, values, positions, seqs, scratch_table, 0, s.num_heads, s.head_dim,
+        ops.qkv_finish(expanded, None, keys, values, positions, seqs, scratch_table, 0, s.num_heads, head_dim,
                        s.v_head_dim, block_size)
         ops_d.attention_prefill_tc(q, keys, values, scratch_table, step.cu_q, step.ctx_after, ctx, step.max_q_len,
-                                   s.num_heads, s.num_heads, s.head_dim, block_size, s.scale)
+                                   s.num_heads, s.num_heads, head_dim, block_size, s.scale, gate=gate,
+                                   gate_stride=gate_stride, sink=sink)
         return True
 
 

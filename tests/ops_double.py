@@ -157,7 +157,7 @@ class DoubleKernels:
 
     def attention_general(self, q, k_cache, v_cache, block_table, positions, token_seq, out, num_heads, num_kv_heads,
                           dim, vdim, block_size, scale, window=0, r1=None, r2=None, gate=None, gate_stride=0,
-                          softcap=0.0, gate_per_element=False, sink=None, value_stride=0):
+                          softcap=0.0, gate_per_element=False, sink=None, value_stride=0, splits=1, scratch_o=None, scratch_ml=None):
         self.calls.append("attention_general")
         n = q.shape[0]
         group = num_heads // num_kv_heads
@@ -268,8 +268,9 @@ class DoubleKernels:
 
     def latent_finish(self, fused, q_plain, q_folded, cache, positions, token_seq, block_table, heads, dim, rope_dim,
                       latent_dim, block_size, rotation=None, rotated=0, latent_offset=0, latent_gamma=None, eps=0.0,
-                      write_cache=True):
+                      write_cache=True, q_whole=None):
         self.calls.append("latent_finish")
+        assert q_whole is None, "whole query heads are the bfloat16 prompt path's"
         n, key_dim = fused.shape[0], latent_dim + rope_dim
         q = fused[:, :heads * (dim + rope_dim)].view(n, heads, dim + rope_dim)
         q_plain.copy_(q[:, :, :dim].reshape(n, heads * dim).to(q_plain.dtype))

@@ -199,6 +199,12 @@ def test_finish_of_the_latent_projection(dtype, shape):
         row = cache[page, 0, positions[t] % block]
         close(row[:rank], latent[t], dtype, f"latent of token {t}")
         close(row[rank:], key_part[t], dtype, f"key part of token {t}")
+    # whole query heads [unrotated | rotated] in one place, for steps that make every head's keys
+    q_whole = torch.empty(n, q_width, dtype=dtype, device="cuda")
+    ops.latent_finish(rows.cuda(), None, None, cache, i32(positions), i32(token_seq), table.cuda(), heads, dim, rope_dim,
+                      rank, block, rotation=table_of(rot, 128), rotated=rot["dims"], write_cache=False, q_whole=q_whole)
+    whole = torch.cat([q[:, :, :dim], plain.rotate(q[:, :, dim:], where, rot)], dim=-1)
+    close(q_whole.view(n, heads, dim + rope_dim), whole, dtype, "whole query heads")
     # a layer that attends over another's cache writes nothing
     before = cache.clone()
     ops.latent_finish(rows.cuda(), q_plain, q_folded, cache, i32([p + 1 for p in positions]), i32(token_seq), table.cuda(),
@@ -248,6 +254,18 @@ def test_attention_with_a_sink_and_a_gate_finds_the_one_key(dtype, shape):
                               gate=gate_rows[first:first + count, 2:], gate_stride=heads + 3, sink=sink.float().cuda(),
                               value_stride=key_dim)
         close(out[:, :heads * rank].view(count, heads, rank), want[first:first + count], dtype, f"tokens {first}..{first + count}")
+    # one token a sequence with the keys cut into parts that run side by side: parts without keys, of one run, of many
+    for splits in (2, 3, 7, 64):
+        for first in (0, 1, 31, 32, 3 * block - 1, 3 * block, T - 1):
+            out = torch.empty(1, heads * rank + 8, dtype=dtype, device="cuda")
+            scratch_o = torch.full((heads * splits * rank,), float("nan"), device="cuda")
+            scratch_ml = torch.full((heads * splits * 2,), float("nan"), device="cuda")
+            ops.attention_general(q[first:first + 1].reshape(1, -1).to(dtype).cuda(), cache, cache, table.cuda(),
+                                  i32([first]), i32([0]), out, heads, 1, key_dim, rank, block, scale,
+                                  gate=gate_rows[first:first + 1, 2:], gate_stride=heads + 3, sink=sink.float().cuda(),
+                                  value_stride=key_dim, splits=splits, scratch_o=scratch_o, scratch_ml=scratch_ml)
+            close(out[:, :heads * rank].view(1, heads, rank), want[first:first + 1], dtype, f"token {first} in {splits} parts")
+            assert float(out[:, heads * rank:].float().abs().max()) == 0.0
     for query, key in marked.items():                             # the marked queries do return the marked key's values
         head_out = want[query, 0] / torch.sigmoid(gate[query, 0].double())
         assert float((head_out - rows[key, :rank].double()).abs().max()) < 0.35 * float(rows[key, :rank].abs().max()), (query, key)
