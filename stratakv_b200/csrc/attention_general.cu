@@ -28,7 +28,8 @@
 namespace skv {
 
 constexpr int GEN_WARPS = 4;
-constexpr int GEN_MAX_VDIM = 512;                 // a lane keeps vdim / 32 accumulators: 8 up to 256, else 16
+constexpr int GEN_MAX_VDIM = 512;
+constexpr int GEN_MERGE_ACC = GEN_MAX_VDIM / 32;   // what a lane of the merge keeps of a row of values                 // a lane keeps vdim / 32 accumulators: 8 up to 256, else 16
 
 constexpr int FINISH_WARPS = 8;
 
@@ -328,24 +329,46 @@ attention_general_merge_kernel(const float* __restrict__ partial_o, const float*
     if (item >= (long long)n_tokens * num_heads) return;
     const int t = (int)(item / num_heads), head = (int)(item % num_heads);
     const float* ml = partial_ml + (size_t)item * splits * 2;
+    // lane s (and s + 32, ...) holds part s's maximum and sum; the weights exp(max_s - top) are made once
     float top = -INFINITY;
-    for (int s = 0; s < splits; ++s) top = fmaxf(top, ml[2 * s]);      // (the first part always has the first key)
+    for (int s = lane; s < splits; s += 32) top = fmaxf(top, ml[2 * s]);      // (the first part always has the first key)
+    top = warp_max(top);
     float total = 0.0f;
-    for (int s = 0; s < splits; ++s) total += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * expf(ml[2 * s] - top);
+    for (int s = lane; s < splits; s += 32) total += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * expf(ml[2 * s] - top);
+    total = warp_sum(total);
     if (sink) total += expf(sink[head] - top);
     float factor = 1.0f / total;
     if (gate && !gate_per_element) factor *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + head]));
     const float* gate_row = gate && gate_per_element ? gate + (size_t)t * gate_stride + (size_t)head * vdim : nullptr;
     T* out_row = out + (size_t)t * out_stride + (size_t)head * vdim;
-    for (int d = lane; d < vdim; d += 32) {
-        float value = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            if (ml[2 * s] == -INFINITY) continue;
-            value = fmaf(partial_o[((size_t)item * splits + s) * vdim + d], expf(ml[2 * s] - top), value);
+    const float* o_parts = partial_o + (size_t)item * splits * vdim;
+    float value[GEN_MERGE_ACC];
+#pragma unroll
+    for (int i = 0; i < GEN_MERGE_ACC; ++i) value[i] = 0.0f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        const int mine = s0 + lane;
+        const float m = mine < splits ? ml[2 * mine] : -INFINITY;
+        const float weight = m == -INFINITY ? 0.0f : expf(m - top) * factor;
+        const int count = min(32, splits - s0);
+        for (int j = 0; j < count; ++j) {
+            const float w = __shfl_sync(0xffffffffu, weight, j);
+            if (w == 0.0f) continue;                                   // (a part without keys left nothing to read)
+            const float* part = o_parts + (size_t)(s0 + j) * vdim;
+#pragma unroll
+            for (int i = 0; i < GEN_MERGE_ACC; ++i) {
+                const int d = lane + 32 * i;
+                if (d < vdim) value[i] = fmaf(part[d], w, value[i]);
+            }
         }
-        value *= factor;
-        if (gate_row) value *= 1.0f / (1.0f + expf(-gate_row[d]));
-        out_row[d] = from_float<T>(value);
+    }
+#pragma unroll
+    for (int i = 0; i < GEN_MERGE_ACC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < vdim) {
+            float v = value[i];
+            if (gate_row) v *= 1.0f / (1.0f + expf(-gate_row[d]));
+            out_row[d] = from_float<T>(v);
+        }
     }
     if (head == num_heads - 1)
         for (int c = num_heads * vdim + lane; c < out_stride; c += 32) out[(size_t)t * out_stride + c] = from_float<T>(0.0f);

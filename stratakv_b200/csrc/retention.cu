@@ -235,12 +235,25 @@ retention_carry_kernel(const float* __restrict__ decay, float* __restrict__ sums
     float S = p_first > 0 ? slot[(size_t)((p_first - 1) & 1) * half_size + mine] : 0.0f;
     const float a = decay[head], log_a = a > 0.0f ? logf(a) : 0.0f;
     const int chunks = (count + RET_CHUNK - 1) / RET_CHUNK;
-    for (int c = 0; c < chunks; ++c) {
-        float* cell = sums + (((size_t)s * max_chunks + c) * H) * (size_t)d * dv + mine;
-        const int L = min(RET_CHUNK, count - c * RET_CHUNK);
-        const float own = *cell;
-        *cell = S;
-        S = fmaf(decay_power(log_a, a, L), S, own);
+    const float whole = decay_power(log_a, a, RET_CHUNK);              // the decay over a full chunk
+    const size_t stride = (size_t)H * d * dv;                          // from a chunk's cell to the next chunk's
+    float* cells = sums + ((size_t)s * max_chunks * H) * (size_t)d * dv + mine;
+    // eight chunks' sums are fetched before any state is stored over them: a store between two loads of the same
+    // array would make each load wait for the one before, and the walk would take a memory latency per chunk
+    constexpr int AHEAD = 8;
+    for (int c0 = 0; c0 < chunks; c0 += AHEAD) {
+        float own[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) own[i] = c0 + i < chunks ? __ldcg(cells + (size_t)(c0 + i) * stride) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) {
+            const int c = c0 + i;
+            if (c < chunks) {
+                cells[(size_t)c * stride] = S;
+                const int L = min(RET_CHUNK, count - c * RET_CHUNK);
+                S = fmaf(L == RET_CHUNK ? whole : decay_power(log_a, a, L), S, own[i]);
+            }
+        }
     }
     slot[(size_t)(p_last & 1) * half_size + mine] = S;
 }

@@ -185,10 +185,10 @@ class LatentAttention(Mixer):
         ops.headwise_linear(q_plain, self.w_k_up_t, q_folded, s.num_heads, out_head_stride=self.key_dim)
         mixed = rt.workspace.get("latent_ctx", (n, s.num_heads * s.latent_dim), rt.dtype)
         # one token a sequence: few (token, head) pairs over long contexts, so each pair's keys are cut into parts that
-        # run side by side, enough to give every SM a few warps (a part is at least 64 keys)
+        # run side by side, enough to give every SM thirty-odd warps (a part is at least 64 keys)
         splits, scratch_o, scratch_ml = 1, None, None
         if step.is_decode and rt.device.type == "cuda":
-            splits = max(1, min(-(-rt.sm_count * 16 // (n * s.num_heads)), -(-step.max_ctx // 64), 64))
+            splits = max(1, min(-(-rt.sm_count * 32 // (n * s.num_heads)), -(-step.max_ctx // 64), 64))
             if splits > 1:
                 scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.latent_dim,), torch.float32)
                 scratch_ml = rt.workspace.get("attn_split_ml", (n * s.num_heads * splits * 2,), torch.float32)
