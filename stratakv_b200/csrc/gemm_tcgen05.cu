@@ -1231,12 +1231,9 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
 // The grouped form of the kernel above: `a` [rows, K] sorted by group, `w` [groups, N, K], `out` [rows, N] (bfloat16
 // with the activation, or float).  The threads store their rows themselves (a tile's rows past its group are another
 // group's).  Blocks beyond the tiles there turn out to be leave at once.
-int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
-                           int groups, int N, int K, act_t act, int* flag, cudaStream_t stream) {
-    constexpr int BN = 128, STAGES = 4;
-    if (K % 8 != 0) return fail("skv_expert_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
-    if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_expert_linear(tcgen05)", "operands must be 16-byte aligned");
-    if ((long long)groups * N > 0x7fffffffLL) return fail("skv_expert_linear(tcgen05)", "too many weight rows");
+template <int BN, int STAGES>
+static int launch_grouped(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
+                          int groups, int N, int K, act_t act, int* flag, cudaStream_t stream) {
     CUtensorMap map_a, map_w;
     if (int code = tensor_map(a, rows, K, 2, TC_BM, TC_BK, &map_a)) return code;
     if (int code = tensor_map(w, groups * N, K, 2, BN, TC_BK, &map_w)) return code;
@@ -1257,6 +1254,20 @@ int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, voi
     const int mode = out_is_float ? TC_MODE_STORE_F32 : TC_MODE_STORE;
     return launch_pdl("skv_expert_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
                       map_a, map_w, map_a, 0, out, rows, N, K, mode, act, flag, RopeArgs{}, GroupArgs{offsets, groups});
+}
+
+int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
+                           int groups, int N, int K, act_t act, int* flag, cudaStream_t stream) {
+    if (K % 8 != 0) return fail("skv_expert_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
+    if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_expert_linear(tcgen05)", "operands must be 16-byte aligned");
+    if ((long long)groups * N > 0x7fffffffLL) return fail("skv_expert_linear(tcgen05)", "too many weight rows");
+    // Tiles 256 columns wide keep the tensor pipe busier (wider MMAs, half the epilogues a FLOP) where the groups have
+    // rows for them; few rows (a decode step) are bound by streaming the weights, and narrow tiles spread those over
+    // more blocks.
+    const long long wide_tiles = ((long long)(rows + TC_BM - 1) / TC_BM + groups) * ((N + 255) / 256);
+    if (N >= 256 && rows >= 2 * TC_BM * groups && wide_tiles >= tc_sm_count())
+        return launch_grouped<256, 4>(a, w, offsets, out, out_is_float, rows, groups, N, K, act, flag, stream);
+    return launch_grouped<128, 4>(a, w, offsets, out, out_is_float, rows, groups, N, K, act, flag, stream);
 }
 
 // The two-block form: clusters of two blocks, as many as the GPU runs at once (74 on 148 SMs), walk the 256 x 256 tiles.
