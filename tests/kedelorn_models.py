@@ -73,7 +73,14 @@ KC = config(300, 128, [retention(2, 128, 64, (0.99, 0.999), rotation(128, 10000.
                        latent(2, 64, 32, 32, 64, 0.1, rotation(32, 20000.0, (4.0, 256, 32.0, 1.0)), None, kv_from=1),
                        retention(4, 32, 160, (0.5, 0.9, 0.99, 1.0), rotation(16, 500.0), moe(64, 16, 1, 2.5, shared=72))],
             streams=1)
-KEDELORN = {"KA": KA, "KB": KB, "KC": KC}
+# KD: two streams; both latent layers have heads whose unrotated and rotated parts together are as wide as their values,
+#     64 numbers, the size at which prompts in bfloat16 make every head's keys and attend on the tensor cores; the
+#     second one borrows the first one's cache across a retention layer, with other heads; twelve experts of which two.
+ROTATED_SIXTEEN = rotation(16, 20000.0, (4.0, 128, 16.0, 1.0))
+KD = config(160, 64, [latent(2, 48, 16, 64, 32, 0.12, ROTATED_SIXTEEN, moe(24, 12, 2, 2.0, shared=32)),
+                      retention(2, 16, 16, (0.984375, 0.998046875), rotation(16, 1e6), moe(24, 12, 2, 2.0, shared=32)),
+                      latent(3, 48, 16, 64, 32, 0.1, ROTATED_SIXTEEN, moe(24, 12, 2, 2.0, shared=32), kv_from=0)], streams=2)
+KEDELORN = {"KA": KA, "KB": KB, "KC": KC, "KD": KD}
 
 
 def make_folder(folder, raw_config, seed, dtype=torch.float32):
