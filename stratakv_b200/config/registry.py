@@ -66,4 +66,10 @@ def load_config(model_dir):
         raise ConfigError("config.json: 'architectures' must be a non-empty list of names "
                           "(or 'architecture' one name)")
     arch = resolve_architecture(archs[0])
-    return arch, arch.config_class.from_dict(raw)
+    config = arch.config_class.from_dict(raw)
+    if getattr(config, "needs_tensor_shapes", None) is not None and config.needs_tensor_shapes():
+        # a size that config.json leaves to the tensors' shapes: the checkpoint's header has it
+        from ..weights.loader import tensor_shapes
+        folder = Path(model_dir)
+        config = config.with_tensor_shapes(tensor_shapes(folder if folder.is_dir() else folder.parent))
+    return arch, config

@@ -23,7 +23,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent
 SOURCES = ("elementwise.cu", "linear.cu", "gemm_tcgen05.cu", "attention.cu", "attention_general.cu", "attention_decode.cu", "attention_decode_fused.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "sampling.cu",
            "stream_ops.cu", "headwise_linear.cu", "recurrent.cu", "stream_mix.cu", "retention.cu", "latent_finish.cu",
-           "routed_mlp.cu")
+           "routed_mlp.cu", "short_conv.cu", "time_mix.cu")
 HEADERS = ("common.cuh",)
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 COMMON_FLAGS = ("-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden")

@@ -342,6 +342,14 @@ __global__ void add_inplace_kernel(float* __restrict__ out, const float* __restr
         out[i] += in[i];
 }
 
+// out[i] += factor * in[i]  (a branch that joins the stream with a weight; the embedding's output added again)
+__global__ void add_scaled_kernel(float* __restrict__ out, const float* __restrict__ in, float factor, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = fmaf(factor, in[i], out[i]);
+}
+
 // x[i] *= factor  (a head that scales its logits)
 __global__ void scale_inplace_kernel(float* __restrict__ x, float factor, size_t n) {
     pdl_launch_dependents();
@@ -478,6 +486,15 @@ SKV_EXPORT int skv_scale_inplace(float* x, float factor, long long n, cudaStream
     long long blocks = (n + 255) / 256;
     if (blocks > sm_count() * 16) blocks = sm_count() * 16;
     return launch_pdl("skv_scale_inplace", scale_inplace_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, factor,
+                      (size_t)n);
+}
+
+SKV_EXPORT int skv_add_scaled(float* out, const float* in, float factor, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!out || !in) return fail("skv_add_scaled", "both rows are needed");
+    long long blocks = (n + 255) / 256;
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    return launch_pdl("skv_add_scaled", add_scaled_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, out, in, factor,
                       (size_t)n);
 }
 

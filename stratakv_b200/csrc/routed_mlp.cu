@@ -1,9 +1,12 @@
 // A routed feed-forward (mixture of experts): router, sort of the (token, choice) pairs by expert, projections over
 // the sorted pairs with each expert's own weights, and the weighted sum.
 //
-//   s = sigmoid(router . h)                     float sums, one score per expert
-//   chosen: the `top` largest s + correction    (the lower index among equals; the correction chooses only)
-//   weight of a chosen expert: s * scale        (renormalize: s divided by the chosen scores' sum first)
+//   s = sigmoid(router . h)                     float sums, one score per expert (or softmax over all experts)
+//   chosen: the `top` largest s + correction    (the lower index among equals; the correction chooses only); with
+//                                               groups: the experts form equal groups of neighbours, a group scores
+//                                               what its best expert does, and only the `keep` best groups' experts
+//                                               can be chosen
+//   weight of a chosen expert: s * scale        (renormalize: s divided by the chosen scores' sum + renorm_eps first)
 //   share = sigmoid(shared_gate . h)            one number per token for a shared expert, if the layer has one
 //
 // Nothing is read back to the host: the number of pairs of every expert stays on the device (offsets [experts + 1]),
@@ -21,7 +24,8 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_tokens_kernel(const T* __restrict__ h, const T* __restrict__ router, const float* __restrict__ correction,
                     const T* __restrict__ shared_gate, int hidden, int experts, int top, float scale, int renormalize,
-                    int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ share) {
+                    int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ share, int softmax,
+                    int groups, int keep, float renorm_eps) {
     extern __shared__ __align__(16) float route_smem[];
     float* row = route_smem;                  // [hidden]
     float* score = row + hidden;              // [experts]
@@ -39,7 +43,7 @@ route_tokens_kernel(const T* __restrict__ h, const T* __restrict__ router, const
         for (int w = lane; w < hidden; w += 32) acc = fmaf(to_float(w_row[w]), row[w], acc);
         acc = warp_sum(acc);
         if (lane == 0) {
-            const float s = 1.0f / (1.0f + expf(-acc));
+            const float s = softmax && e < experts ? acc : 1.0f / (1.0f + expf(-acc));
             if (e < experts) {
                 score[e] = s;
                 choice[e] = correction ? s + correction[e] : s;
@@ -50,6 +54,65 @@ route_tokens_kernel(const T* __restrict__ h, const T* __restrict__ router, const
     }
     __syncthreads();
     if (warp != 0) return;
+    if (softmax) {
+        // the logits become exp(z - max) / sum over all experts
+        float top_logit = -INFINITY;
+        for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, score[e]);
+        top_logit = warp_max(top_logit);
+        float total = 0.0f;
+        for (int e = lane; e < experts; e += 32) {
+            const float w = expf(score[e] - top_logit);
+            score[e] = w;
+            total += w;
+        }
+        total = warp_sum(total);
+        __syncwarp();
+        for (int e = lane; e < experts; e += 32) {
+            const float s = score[e] / total;
+            score[e] = s;
+            choice[e] = correction ? s + correction[e] : s;
+        }
+        __syncwarp();
+    }
+    if (groups > 1) {
+        // `keep` rounds: the group whose best expert scores most (the lower index among equals) is kept, which an
+        // infinity in its members' places says; the members of all other groups then leave the choice
+        const int size = experts / groups;
+        for (int round = 0; round < keep; ++round) {
+            float best = 0.0f;
+            int best_at = -1;
+            for (int g = lane; g < groups; g += 32) {
+                bool taken = false;
+                for (int e = 0; e < size; ++e) taken = taken || choice[g * size + e] == INFINITY;
+                if (taken) continue;
+                float top_score = choice[g * size];
+                for (int e = 1; e < size; ++e) top_score = fmaxf(top_score, choice[g * size + e]);
+                if (best_at < 0 || top_score > best) {
+                    best = top_score;
+                    best_at = g;
+                }
+            }
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+                const int other_at = __shfl_xor_sync(0xffffffffu, best_at, offset);
+                if (other_at >= 0 && (best_at < 0 || other > best || (other == best && other_at < best_at))) {
+                    best = other;
+                    best_at = other_at;
+                }
+            }
+            __syncwarp();
+            if (best_at >= 0)
+                for (int e = lane; e < size; e += 32) choice[best_at * size + e] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < experts; e += 32) {
+            const float c = choice[e];
+            const float s = score[e];
+            choice[e] = c == INFINITY ? (correction ? s + correction[e] : s) : __int_as_float(0x7fc00000);
+        }
+        __syncwarp();
+    }
     // `top` rounds: the largest choice score left (the lower index among equals); an expert that has been taken is
     // marked with a value that is not a number, which the search passes over
     float picked_sum = 0.0f;
@@ -86,7 +149,7 @@ route_tokens_kernel(const T* __restrict__ h, const T* __restrict__ router, const
     }
     if (lane < top) {
         float w = weights[(size_t)t * top + lane];
-        if (renormalize) w = w / picked_sum;
+        if (renormalize) w = w / (picked_sum + renorm_eps);
         weights[(size_t)t * top + lane] = w * scale;
     }
 }
@@ -169,12 +232,15 @@ __device__ __forceinline__ void find_tile(const int* __restrict__ offsets, int e
     }
 }
 
-template <typename TIn, typename TOut>
+// GATED: an expert's weight holds 2 N rows, in tiles of 16 (8 gate rows, then the 8 up rows that go with them, as the
+// dense gated feed-forward packs them); out[., o] = act(gate_o . a) * (up_o . a).
+template <typename TIn, typename TOut, bool GATED>
 __global__ void __launch_bounds__(256)
 expert_linear_kernel(const TIn* __restrict__ a, int a_stride, const int* __restrict__ rows, const TIn* __restrict__ w,
                      const int* __restrict__ offsets, TOut* __restrict__ out, int experts, int N, int K, int act) {
     __shared__ float as[EXP_ROWS][EXP_K + 1];
     __shared__ float ws[EXP_OUTS][EXP_K + 1];
+    __shared__ float us[GATED ? EXP_OUTS : 1][EXP_K + 1];
     __shared__ int source[EXP_ROWS];
     __shared__ int tile_info[3];
     pdl_launch_dependents();
@@ -191,8 +257,9 @@ expert_linear_kernel(const TIn* __restrict__ a, int a_stride, const int* __restr
     __syncthreads();
     const int o0 = blockIdx.x * EXP_OUTS;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const TIn* w_e = w + (size_t)expert * N * K;
+    const TIn* w_e = w + (size_t)expert * (GATED ? 2 : 1) * N * K;
     float acc[2][4] = {};
+    float up[GATED ? 2 : 1][4] = {};
     for (int k0 = 0; k0 < K; k0 += EXP_K) {
         for (int idx = threadIdx.x; idx < EXP_ROWS * EXP_K; idx += 256) {
             const int r = idx / EXP_K, k = idx % EXP_K;
@@ -202,7 +269,13 @@ expert_linear_kernel(const TIn* __restrict__ a, int a_stride, const int* __restr
         for (int idx = threadIdx.x; idx < EXP_OUTS * EXP_K; idx += 256) {
             const int r = idx / EXP_K, k = idx % EXP_K;
             const int o = o0 + r;
-            ws[r][k] = o < N && k0 + k < K ? to_float(w_e[(size_t)o * K + k0 + k]) : 0.0f;
+            if (GATED) {
+                const size_t gate_row = (size_t)(o >> 3) * 16 + (o & 7);
+                ws[r][k] = o < N && k0 + k < K ? to_float(w_e[gate_row * K + k0 + k]) : 0.0f;
+                us[r][k] = o < N && k0 + k < K ? to_float(w_e[(gate_row + 8) * K + k0 + k]) : 0.0f;
+            } else {
+                ws[r][k] = o < N && k0 + k < K ? to_float(w_e[(size_t)o * K + k0 + k]) : 0.0f;
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -213,6 +286,11 @@ expert_linear_kernel(const TIn* __restrict__ a, int a_stride, const int* __restr
                 const float b = ws[tx + 16 * j][k];
                 acc[0][j] = fmaf(a0, b, acc[0][j]);
                 acc[1][j] = fmaf(a1, b, acc[1][j]);
+                if (GATED) {
+                    const float c = us[tx + 16 * j][k];
+                    up[0][j] = fmaf(a0, c, up[0][j]);
+                    up[1][j] = fmaf(a1, c, up[1][j]);
+                }
             }
         }
         __syncthreads();
@@ -229,6 +307,7 @@ expert_linear_kernel(const TIn* __restrict__ a, int a_stride, const int* __restr
             if (act == ACT_RELU2) v = relu_squared(v);
             else if (act == ACT_GELU_TANH) v = gelu_tanh(v);
             else if (act == ACT_SILU) v = v / (1.0f + expf(-v));
+            if (GATED) v *= up[i][j];
             out[(size_t)(first + r) * N + o] = from_float<TOut>(v);
         }
     }
@@ -289,12 +368,15 @@ using namespace skv;
 // [experts] or null.  chosen int [n, top], weights float [n, top], share float [n] (with shared_gate).
 SKV_EXPORT int skv_route_tokens(const void* h, const void* router, const float* correction, const void* shared_gate,
                                 int n, int hidden, int experts, int top, float scale, int renormalize, int* chosen,
-                                float* weights, float* share, cudaStream_t stream) {
+                                float* weights, float* share, int softmax, int groups, int keep, float renorm_eps,
+                                cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hidden <= 0 || experts <= 0 || experts > ROUTE_MAX_EXPERTS || top <= 0 || top > experts || top > ROUTE_MAX_TOP)
         return fail("skv_route_tokens", "1 to 16 of 1 to 1024 experts are served");
     if (!h || !router || !chosen || !weights || (shared_gate && !share))
         return fail("skv_route_tokens", "the rows, the router and places for the choice are needed");
+    if (groups > 1 && (experts % groups != 0 || keep <= 0 || keep > groups || keep * (experts / groups) < top))
+        return fail("skv_route_tokens", "groups must divide the experts, and the kept groups must hold the choices");
     const size_t smem = (size_t)(hidden + 2 * experts) * sizeof(float);
     auto kernel = route_tokens_kernel<skv_t>;
     if (smem > 48 * 1024) {
@@ -304,7 +386,7 @@ SKV_EXPORT int skv_route_tokens(const void* h, const void* router, const float* 
     }
     return launch_pdl("skv_route_tokens", kernel, dim3(n), dim3(ROUTE_THREADS), smem, stream, (const skv_t*)h,
                       (const skv_t*)router, correction, (const skv_t*)shared_gate, hidden, experts, top, scale,
-                      renormalize, chosen, weights, share);
+                      renormalize, chosen, weights, share, softmax, groups, keep, renorm_eps);
 }
 
 SKV_EXPORT int skv_sort_by_expert(const int* chosen, int pairs, int top, int experts, int* offsets, int* order,
@@ -317,28 +399,37 @@ SKV_EXPORT int skv_sort_by_expert(const int* chosen, int pairs, int top, int exp
 
 // a [a_rows, a_stride] and w [experts, N, K] in the compute dtype; rows int [pairs] or null (row p reads a[p]);
 // out [pairs, N] float (out_is_float) or the compute dtype; act: an activation's code or -1 for none.
+// gated: w is [experts, 2 N, K], tiles of 8 gate rows and their 8 up rows; out = act(gate . a) * (up . a).
 // In bfloat16, rows that lie in sorted order already (rows null, a_stride = K) with K a multiple of 8 go to the
 // tensor-memory GEMM's grouped form; `flag` is where its bounded waits report that they gave up.
 SKV_EXPORT int skv_expert_linear(const void* a, int a_stride, int a_rows, const int* rows, const void* w,
                                  const int* offsets, void* out, int out_is_float, int pairs, int experts, int N, int K,
-                                 int act, int* flag, cudaStream_t stream) {
+                                 int act, int gated, int* flag, cudaStream_t stream) {
     if (pairs <= 0) return 0;
     if (experts <= 0 || experts > ROUTE_MAX_EXPERTS || N <= 0 || K <= 0 || a_stride < K || a_rows <= 0)
         return fail("skv_expert_linear", "sizes do not agree");
     if (!a || !w || !offsets || !out) return fail("skv_expert_linear", "rows, weights, offsets and a place for the result are needed");
     if (act >= ACT_SWIGLU_CLAMP) return fail("skv_expert_linear", "this activation is not served");
+    if (gated && (act < 0 || N % 8 != 0)) return fail("skv_expert_linear", "a gated weight needs an activation and whole tiles of 8 rows");
 #if SKV_DTYPE == SKV_BF16
-    if (!rows && a_stride == K && K % 8 == 0 && a_rows >= pairs && !(((uintptr_t)a | (uintptr_t)w) & 15))
+    if (!gated && !rows && a_stride == K && K % 8 == 0 && a_rows >= pairs && !(((uintptr_t)a | (uintptr_t)w) & 15))
         return grouped_linear_tcgen05(a, w, offsets, out, out_is_float, pairs, experts, N, K,
                                       act >= 0 ? ((act_t)act | ACT_ON_STORE) : (act_t)0, flag, stream);
 #endif
     const int row_tiles = (pairs + EXP_ROWS - 1) / EXP_ROWS + experts;       // no expert leaves more than one part tile
     if (row_tiles > 65535) return fail("skv_expert_linear", "too many rows for one launch");
     const dim3 grid((N + EXP_OUTS - 1) / EXP_OUTS, row_tiles);
+    if (gated) {
+        if (out_is_float)
+            return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, float, true>, grid, dim3(256), 0, stream,
+                              (const skv_t*)a, a_stride, rows, (const skv_t*)w, offsets, (float*)out, experts, N, K, act);
+        return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, skv_t, true>, grid, dim3(256), 0, stream,
+                          (const skv_t*)a, a_stride, rows, (const skv_t*)w, offsets, (skv_t*)out, experts, N, K, act);
+    }
     if (out_is_float)
-        return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, float>, grid, dim3(256), 0, stream,
+        return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, float, false>, grid, dim3(256), 0, stream,
                           (const skv_t*)a, a_stride, rows, (const skv_t*)w, offsets, (float*)out, experts, N, K, act);
-    return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, skv_t>, grid, dim3(256), 0, stream,
+    return launch_pdl("skv_expert_linear", expert_linear_kernel<skv_t, skv_t, false>, grid, dim3(256), 0, stream,
                       (const skv_t*)a, a_stride, rows, (const skv_t*)w, offsets, (skv_t*)out, experts, N, K, act);
 }
 

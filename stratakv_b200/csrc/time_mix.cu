@@ -1,0 +1,257 @@
+// Time mixing with a matrix state per head and a decay per token and key channel (the RWKV family's mixer), over packed
+// steps of several sequences.  For a sequence's token at position p, with h' the token before's input (zeros at p = 0):
+//
+//   mix_s = h + (h' - h) * mu_s                     one mix per projection s (token_shift_mix)
+//   r, k, v, gate logits, decay logits               the library's projections of those mixes
+//   w     = exp(-exp(W2 tanh(lora) + w0))            time_mix_decay; lora = W1 mix_w
+//   o_p   = (S_(p-1) + diag(u) k_p v_p^T)^T r_p      time_mix_scan; S is [key channel][value channel] per head
+//   S_p   = diag(w_p) S_(p-1) + k_p v_p^T
+//   out_p = o_p / rms(o_p) per head * norm * silu(gate) * out_scale      time_mix_finish (compute dtype: the input of
+//                                                                        the output projection)
+//
+// Everything between the projections is float.  Per sequence the cache keeps float state, one row per slot, starting
+// `state_offset` floats into the row:
+//   [2][heads][dim][dim]  S after the sequence's last position, in the half chosen by that position's parity: a step
+//                         reads the half of the position before its first token and writes the half of its last, so a
+//                         one-token step that runs twice (a graph's capture after its warm-up) computes the same thing;
+//   [2][hidden]           the mixer's input at the last position, by the same rule.  token_shift_mix reads it and the
+//                         scan, which runs later in the same step, writes it: no kernel reads what it writes.
+// A sequence's first token (position 0) ignores the state, so a slot's earlier user leaves nothing behind.
+#include "common.cuh"
+
+namespace skv {
+
+struct TimeMixBatch {
+    const int* positions;      // [tokens]
+    const int* token_seq;      // [tokens]
+    const int* cu_q;           // [seqs + 1]
+    const int* slot_ids;       // [seqs]
+    float* state;              // [slots][state_stride] floats
+    long long state_stride;    // floats per slot
+    long long state_offset;    // where this mixer's state starts within a slot's row
+};
+
+constexpr int TM_MAX_MIXES = 8;
+constexpr int TM_REGS = 16;            // key channels of one value column that a thread of the scan keeps
+
+// mixes[s][t][c] = h[t][c] + (before[t][c] - h[t][c]) * mu[s][c]; a block per token, threads over the channels.
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ mu, T* __restrict__ mixes, int n_tokens,
+                       int hidden, int n_mixes, long long before_offset, const TimeMixBatch batch) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int p = batch.positions[t], s = batch.token_seq[t];
+    const bool inside = t > batch.cu_q[s];
+    const float* kept = batch.state + (size_t)batch.slot_ids[s] * batch.state_stride + batch.state_offset + before_offset +
+                        (size_t)((p - 1) & 1) * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float now = to_float(h[(size_t)t * hidden + c]);
+        const float before = inside ? to_float(h[(size_t)(t - 1) * hidden + c]) : (p > 0 ? kept[c] : 0.0f);
+        const float delta = before - now;
+        for (int m = 0; m < n_mixes; ++m)
+            mixes[((size_t)m * n_tokens + t) * hidden + c] = from_float<T>(fmaf(delta, mu[(size_t)m * hidden + c], now));
+    }
+}
+
+// decay[t][c] = exp(-exp(w0[c] + sum_j w2[c][j] * tanh(lora[t][j]))); a block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+time_mix_decay_kernel(const float* __restrict__ lora, int lora_stride, int rank, const T* __restrict__ w2,
+                      const float* __restrict__ w0, float* __restrict__ decay, int channels) {
+    extern __shared__ __align__(16) float tm_lora[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) tm_lora[j] = tanhf(lora[(size_t)t * lora_stride + j]);
+    __syncthreads();
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const T* row = w2 + (size_t)c * rank;
+        float z = w0[c];
+        for (int j = 0; j < rank; ++j) z = fmaf(to_float(row[j]), tm_lora[j], z);
+        decay[(size_t)t * channels + c] = expf(-expf(z));
+    }
+}
+
+// The recurrence.  A block per (sequence, head, slice of value columns); thread (column c, part s of `key_split`) keeps
+// S[i][c] for the key channels i = s, s + key_split, ...; the token's r, k, w (whole head) and v (the block's columns)
+// are staged in shared memory a few tokens at a time.  The head-0 block of a sequence's first slice also remembers the
+// mixer's input at the sequence's last token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
+                     const float* __restrict__ decay, int stride, const float* __restrict__ bonus,
+                     float* __restrict__ out, const T* __restrict__ h, int hidden, int heads, int dim, int key_split,
+                     int cols, int chunk, const TimeMixBatch batch) {
+    extern __shared__ __align__(16) float tm_stage[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * cols;
+    const int first = batch.cu_q[seq], n = batch.cu_q[seq + 1] - first;
+    if (n <= 0) return;
+    const int p0 = batch.positions[first];
+    float* slot_state = batch.state + (size_t)batch.slot_ids[seq] * batch.state_stride + batch.state_offset;
+    const size_t half = (size_t)heads * dim * dim;
+    const float* s_read = slot_state + (size_t)((p0 - 1) & 1) * half + (size_t)head * dim * dim;
+    float* s_write = slot_state + (size_t)((p0 + n - 1) & 1) * half + (size_t)head * dim * dim;
+    const int part = threadIdx.x % key_split, c = threadIdx.x / key_split, col = col0 + c;
+    const bool active = c < cols && col < dim;
+    float S[TM_REGS], u[TM_REGS];
+#pragma unroll
+    for (int j = 0; j < TM_REGS; ++j) {
+        const int i = j * key_split + part;
+        const bool held = active && i < dim;
+        S[j] = held && p0 > 0 ? s_read[(size_t)i * dim + col] : 0.0f;
+        u[j] = held ? bonus[(size_t)head * dim + i] : 0.0f;
+    }
+    float* sr = tm_stage;                       // [chunk][dim]
+    float* sk = sr + (size_t)chunk * dim;
+    float* sw = sk + (size_t)chunk * dim;
+    float* sv = sw + (size_t)chunk * dim;       // [chunk][cols]
+    for (int t0 = 0; t0 < n; t0 += chunk) {
+        const int m = min(chunk, n - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < m * dim; idx += blockDim.x) {
+            const int tok = idx / dim, i = idx - tok * dim;
+            const size_t at = (size_t)(first + t0 + tok) * stride + (size_t)head * dim + i;
+            sr[idx] = r[at];
+            sk[idx] = k[at];
+            sw[idx] = decay[at];
+        }
+        for (int idx = threadIdx.x; idx < m * cols; idx += blockDim.x) {
+            const int tok = idx / cols, j = idx - tok * cols;
+            sv[idx] = col0 + j < dim ? v[(size_t)(first + t0 + tok) * stride + (size_t)head * dim + col0 + j] : 0.0f;
+        }
+        __syncthreads();
+        for (int tok = 0; tok < m; ++tok) {
+            const float vj = active ? sv[tok * cols + c] : 0.0f;
+            const float* rr = sr + (size_t)tok * dim;
+            const float* kk = sk + (size_t)tok * dim;
+            const float* ww = sw + (size_t)tok * dim;
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < TM_REGS; ++j) {
+                const int i = j * key_split + part;
+                if (i < dim) {
+                    const float kv = kk[i] * vj;
+                    acc = fmaf(rr[i], fmaf(u[j], kv, S[j]), acc);
+                    S[j] = fmaf(ww[i], S[j], kv);
+                }
+            }
+            for (int offset = key_split >> 1; offset > 0; offset >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, offset);
+            if (part == 0 && active) out[(size_t)(first + t0 + tok) * stride + (size_t)head * dim + col] = acc;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < TM_REGS; ++j) {
+        const int i = j * key_split + part;
+        if (active && i < dim) s_write[(size_t)i * dim + col] = S[j];
+    }
+    if (head == 0 && blockIdx.z == 0) {
+        float* kept = slot_state + 2 * half + (size_t)((p0 + n - 1) & 1) * hidden;
+        const T* last = h + (size_t)(first + n - 1) * hidden;
+        for (int w = threadIdx.x; w < hidden; w += blockDim.x) kept[w] = to_float(last[w]);
+    }
+}
+
+// out[t][head] = o / rms(o) * norm * silu(gate) * out_scale; a warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+time_mix_finish_kernel(const float* __restrict__ o, const float* __restrict__ gate, int stride,
+                       const float* __restrict__ norm, float eps, float out_scale, T* __restrict__ out, int out_stride,
+                       int n_tokens, int heads, int dim) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads), head = (int)(item - (long long)t * heads);
+    const float* row = o + (size_t)t * stride + (size_t)head * dim;
+    const float* g = gate + (size_t)t * stride + (size_t)head * dim;
+    float squares = 0.0f;
+    for (int d = lane; d < dim; d += 32) squares = fmaf(row[d], row[d], squares);
+    const float factor = out_scale / sqrtf(warp_sum(squares) / (float)dim + eps);
+    for (int d = lane; d < dim; d += 32) {
+        const float z = g[d];
+        out[(size_t)t * out_stride + (size_t)head * dim + d] =
+            from_float<T>(row[d] * factor * norm[(size_t)head * dim + d] * (z / (1.0f + expf(-z))));
+    }
+    if (head == heads - 1)                              // columns that pad the row to whole 16 bytes
+        for (int d = heads * dim + lane; d < out_stride; d += 32) out[(size_t)t * out_stride + d] = from_float<T>(0.0f);
+}
+
+}  // namespace skv
+
+using namespace skv;
+
+static TimeMixBatch time_mix_batch(const int* positions, const int* token_seq, const int* cu_q, const int* slot_ids,
+                                   float* state, long long state_stride, long long state_offset) {
+    TimeMixBatch batch;
+    batch.positions = positions; batch.token_seq = token_seq; batch.cu_q = cu_q; batch.slot_ids = slot_ids;
+    batch.state = state; batch.state_stride = state_stride; batch.state_offset = state_offset;
+    return batch;
+}
+
+// Floats of state a sequence needs: S twice and the mixer's last input twice.
+SKV_EXPORT long long skv_time_mix_state_floats(int hidden, int heads, int dim) {
+    return 2LL * heads * dim * dim + 2LL * hidden;
+}
+
+// h [n, hidden] and mixes [n_mixes, n, hidden] in the compute dtype, mu float [n_mixes, hidden].
+SKV_EXPORT int skv_token_shift_mix(const void* h, const float* mu, void* mixes, int n, int hidden, int n_mixes, int heads,
+                                   int dim, const int* positions, const int* token_seq, const int* cu_q,
+                                   const int* slot_ids, float* state, long long state_stride, long long state_offset,
+                                   cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (hidden <= 0 || n_mixes <= 0 || n_mixes > TM_MAX_MIXES) return fail("skv_token_shift_mix", "1 to 8 mixes are served");
+    if (!h || !mu || !mixes || !state) return fail("skv_token_shift_mix", "rows, factors, state and a place for the mixes are needed");
+    return launch_pdl("skv_token_shift_mix", token_shift_mix_kernel<skv_t>, dim3(n), dim3(256), 0, stream,
+                      (const skv_t*)h, mu, (skv_t*)mixes, n, hidden, n_mixes, 2LL * heads * dim * dim,
+                      time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset));
+}
+
+// lora float [n, lora_stride] (the first `rank` columns count), w2 [channels, rank] in the compute dtype.
+SKV_EXPORT int skv_time_mix_decay(const float* lora, int lora_stride, int rank, const void* w2, const float* w0,
+                                  float* decay, int n, int channels, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (rank <= 0 || rank > 8192 || channels <= 0 || lora_stride < rank) return fail("skv_time_mix_decay", "sizes do not agree");
+    if (!lora || !w2 || !w0 || !decay) return fail("skv_time_mix_decay", "a pointer is missing");
+    return launch_pdl("skv_time_mix_decay", time_mix_decay_kernel<skv_t>, dim3(n), dim3(256), (size_t)rank * sizeof(float),
+                      stream, lora, lora_stride, rank, (const skv_t*)w2, w0, decay, channels);
+}
+
+// r, k, v, decay, out: float [n, stride] with head `a` at columns a * dim; bonus float [heads, dim]; h [n, hidden] in the
+// compute dtype.
+SKV_EXPORT int skv_time_mix_scan(const float* r, const float* k, const float* v, const float* decay, int stride,
+                                 const float* bonus, float* out, const void* h, int hidden, int n_seqs, int heads, int dim,
+                                 const int* positions, const int* token_seq, const int* cu_q, const int* slot_ids,
+                                 float* state, long long state_stride, long long state_offset, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (heads <= 0 || dim <= 0 || dim > 32 * TM_REGS || heads > 65535)
+        return fail("skv_time_mix_scan", "heads of 1 to 512 numbers are served");
+    if (!r || !k || !v || !decay || !bonus || !out || !h || !state) return fail("skv_time_mix_scan", "a pointer is missing");
+    int key_split = 1;
+    while (key_split * TM_REGS < dim) key_split *= 2;
+    const int cols = min(dim, 256 / key_split);
+    const int slices = (dim + cols - 1) / cols;
+    int chunk = (int)(40 * 1024 / ((3 * (size_t)dim + cols) * sizeof(float)));
+    chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
+    const size_t smem = (size_t)chunk * (3 * (size_t)dim + cols) * sizeof(float);
+    const int threads = ((cols * key_split + 31) / 32) * 32;
+    return launch_pdl("skv_time_mix_scan", time_mix_scan_kernel<skv_t>, dim3(n_seqs, heads, slices), dim3(threads), smem,
+                      stream, r, k, v, decay, stride, bonus, out, (const skv_t*)h, hidden, heads, dim, key_split, cols,
+                      chunk, time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset));
+}
+
+// o and gate float [n, stride]; norm float [heads * dim]; out [n, out_stride] in the compute dtype.
+SKV_EXPORT int skv_time_mix_finish(const float* o, const float* gate, int stride, const float* norm, float eps,
+                                   float out_scale, void* out, int out_stride, int n, int heads, int dim,
+                                   cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (heads <= 0 || dim <= 0 || out_stride < heads * dim) return fail("skv_time_mix_finish", "sizes do not agree");
+    if (!o || !gate || !norm || !out) return fail("skv_time_mix_finish", "a pointer is missing");
+    const long long items = (long long)n * heads;
+    return launch_pdl("skv_time_mix_finish", time_mix_finish_kernel<skv_t>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0,
+                      stream, o, gate, stride, norm, eps, out_scale, (skv_t*)out, out_stride, n, heads, dim);
+}

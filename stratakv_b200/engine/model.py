@@ -149,7 +149,16 @@ class Model:
         if stats is not None:
             stats.expect(readers[0])
         self.embedding.forward(step, x, self.flags, stats=stats)
+        first = None
+        if any(getattr(entry, "adds_embedding", False) for entry in spec.schedule):
+            # some run adds the embedding's output to the stream again: keep it
+            first = rt.workspace.get("embedding_output", (step.n_tokens, spec.hidden_size), torch.float32)
+            first.copy_(x)
         for index, entry in enumerate(spec.schedule):
+            if first is not None and entry.adds_embedding:
+                rt.kernels().add_scaled(x, first, 1.0)
+                if stats is not None:
+                    stats.invalidate()
             step.norm_after_layer = readers[index + 1]
             following = spec.schedule[index + 1].layer if index + 1 < len(spec.schedule) else None
             step.next_layer_norm = self.layers[following].mixer_norm if following is not None else None

@@ -854,8 +854,12 @@ class Kernels:
 
     # ---- routed feed-forward ------------------------------------------------------------------
     def route_tokens(self, h, router_w, correction, top: int, scale: float, renormalize: bool, chosen, weights,
-                     shared_gate_weight=None, shared_gate_out=None):
-        """Per token: ``s = sigmoid(router_w . h)`` (float32 sums); the ``top`` experts with the largest
+                     shared_gate_weight=None, shared_gate_out=None, softmax: bool = False, groups: int = 0,
+                     keep: int = 0, renorm_eps: float = 0.0):
+        """(``softmax``: the scores are a softmax over all experts instead of sigmoids.  ``groups`` > 1: the experts form
+        that many equal groups of neighbours, a group scores what its best expert does and only experts of the ``keep``
+        best groups can be chosen.  ``renorm_eps`` is added to the chosen scores' sum before ``renormalize`` divides.)
+        Per token: ``s = sigmoid(router_w . h)`` (float32 sums); the ``top`` experts with the largest
         ``s + correction`` (the lower index among equals) into ``chosen`` (int32 ``[tokens, top]``), their ``s * scale``
         into ``weights`` (``renormalize``: divided by the chosen scores' sum first).  With ``shared_gate_weight``
         ``[hidden]``: ``shared_gate_out[t] = sigmoid(shared_gate_weight . h[t])``."""
@@ -876,10 +880,12 @@ class Kernels:
             self._want(shared_gate_weight, self.dtype, "shared_gate_weight"); self._want(shared_gate_out, torch.float32, "shared_gate_out")
             if shared_gate_weight.numel() != hidden or shared_gate_out.numel() != n:
                 raise KernelError("route_tokens: the shared expert's gate has the wrong size")
+        if groups > 1 and (experts % groups or not 0 < keep <= groups or keep * (experts // groups) < top):
+            raise KernelError("route_tokens: groups must divide the experts and the kept groups hold the choices")
         self._check(self.lib.skv_route_tokens(
             _ptr(h), _ptr(router_w), _ptr(correction), _ptr(shared_gate_weight), n, hidden, experts, int(top),
-            ctypes.c_float(scale), int(bool(renormalize)), _ptr(chosen), _ptr(weights), _ptr(shared_gate_out), _stream()),
-            "route_tokens")
+            ctypes.c_float(scale), int(bool(renormalize)), _ptr(chosen), _ptr(weights), _ptr(shared_gate_out),
+            int(bool(softmax)), int(groups), int(keep), ctypes.c_float(renorm_eps), _stream()), "route_tokens")
 
     def sort_by_expert(self, chosen, experts: int, offsets, order, place):
         """A counting sort of the (token, choice) pairs by expert: ``offsets`` (int32 ``[experts + 1]``) bounds each
@@ -906,8 +912,11 @@ class Kernels:
         build's tensor-core form wants neighbouring rows of whole 16 bytes."""
         return self.dtype == torch.bfloat16 and hidden % 8 == 0
 
-    def expert_linear(self, a, w, offsets, out, rows=None, activation: Optional[str] = None, flag=None):
-        """``out[p] = act(w[e] . a[row(p)])`` for every sorted pair p of expert e (``offsets`` from ``sort_by_expert``);
+    def expert_linear(self, a, w, offsets, out, rows=None, activation: Optional[str] = None, flag=None,
+                      gated: bool = False):
+        """(``gated``: ``w`` is ``[experts, 2 N, K]`` in tiles of 8 gate rows and their 8 up rows, as ``pack_gate_up``
+        lays them out, and ``out[p] = act(gate_e . a) * (up_e . a)``.)
+        ``out[p] = act(w[e] . a[row(p)])`` for every sorted pair p of expert e (``offsets`` from ``sort_by_expert``);
         ``w`` ``[experts, N, K]``; ``row(p) = rows[p]`` (the first projection gathers its input from the tokens) or p.
         ``out`` ``[pairs, N]`` is the compute dtype (with ``activation``) or float32.  Sums are float32."""
         self._want(a, self.dtype, "a"); self._want(w, self.dtype, "w"); self._want(offsets, torch.int32, "offsets")
@@ -915,6 +924,10 @@ class Kernels:
             raise KernelError("expert_linear: out must be a contiguous CUDA tensor, float32 or the compute dtype")
         pairs = out.shape[0]
         experts, N, K = w.shape
+        if gated:
+            if N % 16 or activation is None:
+                raise KernelError("expert_linear: a gated weight has whole tiles of 16 rows and an activation")
+            N //= 2
         if a.shape[1] != K or out.shape[1] != N or offsets.numel() != experts + 1 or (rows is None and a.shape[0] != pairs):
             raise KernelError("expert_linear: shapes do not agree")
         if rows is not None:
@@ -926,7 +939,7 @@ class Kernels:
         self._check(self.lib.skv_expert_linear(
             _ptr(a), a.stride(0), a.shape[0], _ptr(rows), _ptr(w), _ptr(offsets), _ptr(out),
             int(out.dtype == torch.float32), pairs, experts, N, K, ACTIVATIONS[activation] if activation is not None else -1,
-            _ptr(flag if flag is not None else self.error_flag), _stream()), "expert_linear")
+            int(bool(gated)), _ptr(flag if flag is not None else self.error_flag), _stream()), "expert_linear")
 
     def combine_experts(self, results, place, weights, shared, share, x, add: bool = True):
         """``x[t] (+)= sum_k weights[t, k] * results[place[t, k]] + share[t] * shared[t]`` (float32; ``shared`` may be
@@ -947,6 +960,154 @@ class Kernels:
                 raise KernelError("combine_experts: one gate per token of the shared expert's result is needed")
         self._check(self.lib.skv_combine_experts(_ptr(results), _ptr(place), _ptr(weights), _ptr(shared), _ptr(share),
                                                  _ptr(x), n, hidden, top, int(bool(add)), _stream()), "combine_experts")
+
+    def add_scaled(self, out, other, factor: float):
+        """``out += factor * other`` (float32)."""
+        self._want(out, torch.float32, "out"); self._want(other, torch.float32, "other")
+        if out.numel() != other.numel():
+            raise KernelError("add_scaled: sizes differ")
+        self._check(self.lib.skv_add_scaled(_ptr(out), _ptr(other), ctypes.c_float(factor),
+                                            ctypes.c_longlong(out.numel()), _stream()), "add_scaled")
+
+    def projection_norm(self, rows, eps: float, segments):
+        """An RMS norm with a weight over whole segments of a fused projection's float32 rows, in place: for each of one
+        or two ``(offset, width, bias or None, weight)``, the columns ``[offset, offset + width)`` plus their bias are
+        divided by their root mean square (eps inside the root) and multiplied by the weight (float32 ``[width]``)."""
+        self._want(rows, torch.float32, "rows")
+        if not 1 <= len(segments) <= 2:
+            raise KernelError("projection_norm: one or two segments")
+        flat = []
+        for offset, width, bias, weight in segments:
+            self._want(weight, torch.float32, "weight")
+            if bias is not None:
+                self._want(bias, torch.float32, "bias")
+            if weight.numel() != width or (bias is not None and bias.numel() != width) or offset + width > rows.shape[1]:
+                raise KernelError("projection_norm: a segment's sizes do not agree")
+            flat += [int(offset), int(width), _ptr(bias), _ptr(weight)]
+        if len(segments) == 1:
+            flat += [0, 0, _NULL, _NULL]
+        self._check(self.lib.skv_projection_norm(_ptr(rows), rows.shape[1], rows.shape[0], ctypes.c_float(eps), *flat,
+                                                 _stream()), "projection_norm")
+
+    @staticmethod
+    def _state_args(step_meta, state, offset_floats: int):
+        """Pointers of a step's packed batch and of a state area ``[slots, bytes]`` whose rows hold a part's floats from
+        ``offset_floats`` on."""
+        positions, token_seq, cu_q, slot_ids = step_meta
+        if state is not None and (state.dtype != torch.float32 or state.dim() != 2 or not state.is_cuda
+                                  or not state.is_contiguous()):
+            raise KernelError("state must be a contiguous float32 [slots, floats] CUDA tensor")
+        for name, tensor in (("positions", positions), ("token_seq", token_seq), ("cu_q", cu_q), ("slot_ids", slot_ids)):
+            if tensor.dtype != torch.int32 or not tensor.is_cuda:
+                raise KernelError(f"{name} must be int32 on the GPU")
+        return (_ptr(positions), _ptr(token_seq), _ptr(cu_q), _ptr(slot_ids), _ptr(state),
+                ctypes.c_longlong(state.shape[1] if state is not None else 0), ctypes.c_longlong(offset_floats))
+
+    def short_conv_rotary(self, rows, bias, conv_w, taps: int, cos_sin, rotated: int, interleaved: bool, block_table,
+                          q_out, k_cache, v_cache, num_heads: int, num_kv_heads: int, dim: int, block_size: int,
+                          write_kv: bool, step_meta, state, state_offset: int = 0):
+        """From float32 rows ``[queries | keys]`` of a fused projection: ``bias`` added, a causal convolution over time on
+        every channel (``conv_w`` float32 ``[channels, taps]``; what lies before the step comes from ``state``), rotary
+        positions on the first ``rotated`` numbers of every head (``cos_sin`` ``[positions, rotated / 2, 2]``; pairs
+        ``(2i, 2i + 1)`` if ``interleaved`` else ``(i, i + rotated / 2)``); queries to ``q_out``, rotated keys to
+        ``k_cache`` and, with ``v_cache``, the convolved keys before rotation there.  ``state`` float32
+        ``[slots, floats]``: from ``state_offset`` a row holds ``[taps, channels]``; ``short_conv_remember`` writes it."""
+        self._want(rows, torch.float32, "rows"); self._want(q_out, self.dtype, "q_out")
+        self._want(k_cache, self.dtype, "k_cache"); self._want(block_table, torch.int32, "block_table")
+        channels = (num_heads + num_kv_heads) * dim
+        n = rows.shape[0]
+        if v_cache is not None:
+            self._want(v_cache, self.dtype, "v_cache")
+            if v_cache.shape != k_cache.shape:
+                raise KernelError("short_conv_rotary: values that are keys are cached in the keys' shape")
+        if rows.shape[1] < channels or tuple(q_out.shape) != (n, num_heads * dim) or \
+                tuple(k_cache.shape[1:]) != (num_kv_heads, block_size, dim):
+            raise KernelError("short_conv_rotary: shapes do not agree")
+        if bias is not None:
+            self._want(bias, torch.float32, "bias")
+            if bias.numel() != channels:
+                raise KernelError("short_conv_rotary: one bias per channel is needed")
+        if taps > 0:
+            self._want(conv_w, torch.float32, "conv_w")
+            if tuple(conv_w.shape) != (channels, taps):
+                raise KernelError("short_conv_rotary: the convolution's weight must be [channels, taps]")
+        if rotated > 0:
+            self._want(cos_sin, torch.float32, "cos_sin")
+            if cos_sin.dim() != 3 or cos_sin.shape[1] * 2 != rotated or rotated > dim:
+                raise KernelError("short_conv_rotary: the rotation's table must be [positions, rotated / 2, 2]")
+        if taps > 1 and (state is None or state_offset + taps * channels > state.shape[1]):
+            raise KernelError("short_conv_rotary: the state's rows are too short")
+        self._check(self.lib.skv_short_conv_rotary(
+            _ptr(rows), rows.shape[1], _ptr(bias), _ptr(conv_w if taps > 0 else None), int(taps),
+            _ptr(cos_sin if rotated > 0 else None), int(rotated), int(bool(interleaved)), _ptr(block_table),
+            block_table.shape[1], _ptr(q_out), _ptr(k_cache), _ptr(v_cache), n, num_heads, num_kv_heads, dim, block_size,
+            int(bool(write_kv)), *self._state_args(step_meta, state, state_offset), _stream()), "short_conv_rotary")
+
+    def short_conv_remember(self, rows, bias, channels: int, taps: int, n_seqs: int, step_meta, state,
+                            state_offset: int = 0):
+        """The biased projections of every sequence's last ``taps - 1`` positions of the step into its state (row
+        ``position mod taps``); it runs after ``short_conv_rotary`` has read the rows of the positions before the step."""
+        self._want(rows, torch.float32, "rows")
+        if taps <= 1:
+            return
+        self._check(self.lib.skv_short_conv_remember(
+            _ptr(rows), rows.shape[1], _ptr(bias), int(channels), int(taps), int(n_seqs),
+            *self._state_args(step_meta, state, state_offset), _stream()), "short_conv_remember")
+
+    def time_mix_state_floats(self, hidden: int, heads: int, dim: int) -> int:
+        self.lib.skv_time_mix_state_floats.restype = ctypes.c_longlong
+        return int(self.lib.skv_time_mix_state_floats(int(hidden), int(heads), int(dim)))
+
+    def token_shift_mix(self, h, mu, mixes, heads: int, dim: int, step_meta, state, state_offset: int = 0):
+        """``mixes[s, t] = h[t] + (h[t - 1] - h[t]) * mu[s]`` in the compute dtype, with zeros before a sequence's first
+        token and the last token of the step before from ``state`` (``csrc/time_mix.cu`` has its layout)."""
+        self._want(h, self.dtype, "h"); self._want(mixes, self.dtype, "mixes"); self._want(mu, torch.float32, "mu")
+        n, hidden = h.shape
+        if mixes.dim() != 3 or tuple(mixes.shape[1:]) != (n, hidden) or tuple(mu.shape) != (mixes.shape[0], hidden):
+            raise KernelError("token_shift_mix: shapes do not agree")
+        self._check(self.lib.skv_token_shift_mix(
+            _ptr(h), _ptr(mu), _ptr(mixes), n, hidden, mixes.shape[0], int(heads), int(dim),
+            *self._state_args(step_meta, state, state_offset), _stream()), "token_shift_mix")
+
+    def time_mix_decay(self, lora, rank: int, w2, w0, decay):
+        """``decay[t, c] = exp(-exp(w0[c] + w2[c] . tanh(lora[t, :rank])))`` (float32; ``w2`` in the compute dtype)."""
+        self._want(lora, torch.float32, "lora"); self._want(w2, self.dtype, "w2"); self._want(w0, torch.float32, "w0")
+        self._want(decay, torch.float32, "decay")
+        n, channels = decay.shape
+        if lora.shape[0] != n or lora.shape[1] < rank or tuple(w2.shape) != (channels, rank) or w0.numel() != channels:
+            raise KernelError("time_mix_decay: shapes do not agree")
+        self._check(self.lib.skv_time_mix_decay(_ptr(lora), lora.shape[1], int(rank), _ptr(w2), _ptr(w0), _ptr(decay), n,
+                                                channels, _stream()), "time_mix_decay")
+
+    def time_mix_scan(self, r, k, v, decay, bonus, out, h, n_seqs: int, heads: int, dim: int, step_meta, state,
+                      state_offset: int = 0):
+        """Per head ``o_t = (S + diag(bonus) k_t v_t^T)^T r_t``, then ``S <- diag(decay_t) S + k_t v_t^T`` (all float32
+        ``[tokens, heads * dim]``); S and the step's last row of ``h`` are kept in ``state``."""
+        for name, tensor in (("r", r), ("k", k), ("v", v), ("decay", decay), ("out", out)):
+            self._want(tensor, torch.float32, name)
+            if tuple(tensor.shape) != tuple(r.shape):
+                raise KernelError("time_mix_scan: r, k, v, decay and out have one shape")
+        self._want(bonus, torch.float32, "bonus"); self._want(h, self.dtype, "h")
+        if r.shape[1] != heads * dim or bonus.numel() != heads * dim or h.shape[0] != r.shape[0]:
+            raise KernelError("time_mix_scan: shapes do not agree")
+        if state_offset + self.time_mix_state_floats(h.shape[1], heads, dim) > state.shape[1]:
+            raise KernelError("time_mix_scan: the state's rows are too short")
+        self._check(self.lib.skv_time_mix_scan(
+            _ptr(r), _ptr(k), _ptr(v), _ptr(decay), r.shape[1], _ptr(bonus), _ptr(out), _ptr(h), h.shape[1], int(n_seqs),
+            int(heads), int(dim), *self._state_args(step_meta, state, state_offset), _stream()), "time_mix_scan")
+
+    def time_mix_finish(self, o, gate, norm, eps: float, out_scale: float, out, heads: int, dim: int):
+        """``out = o / rms(o) per head * norm * silu(gate) * out_scale`` in the compute dtype (``out`` may be wider than
+        ``heads * dim``; the further columns are set to zero)."""
+        self._want(o, torch.float32, "o"); self._want(gate, torch.float32, "gate"); self._want(norm, torch.float32, "norm")
+        self._want(out, self.dtype, "out")
+        n = o.shape[0]
+        if tuple(o.shape) != (n, heads * dim) or tuple(gate.shape) != (n, heads * dim) or norm.numel() != heads * dim \
+                or out.shape[0] != n or out.shape[1] < heads * dim:
+            raise KernelError("time_mix_finish: shapes do not agree")
+        self._check(self.lib.skv_time_mix_finish(_ptr(o), _ptr(gate), o.shape[1], _ptr(norm), ctypes.c_float(eps),
+                                                 ctypes.c_float(out_scale), _ptr(out), out.shape[1], n, int(heads),
+                                                 int(dim), _stream()), "time_mix_finish")
 
     def scale_inplace(self, x, factor: float):
         self._want(x, torch.float32, "x")

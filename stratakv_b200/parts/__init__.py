@@ -1,6 +1,6 @@
 """Parts a model is put together from.  Importing the package registers the built-in kinds."""
-from . import (attention, block, embedding, ffn, latent_attention, norm, position, recurrent, retention, routed_mlp,  # noqa: F401
-               stream_mix, token_side)
+from . import (attention, block, conv_attention, embedding, ffn, latent_attention, mixer_pair, norm, position,  # noqa: F401
+               recurrent, retention, routed_mlp, stream_mix, time_mix, token_side)
 from .base import (CacheRequest, FeedForward, Mixer, Norm, Part, Runtime, StepBatch, TensorRequest)
 from .registry import (part_class, register_arrangement, register_embedding, register_ffn, register_head,
                        register_mixer, register_norm, register_part, register_position)

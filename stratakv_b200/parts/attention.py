@@ -129,6 +129,10 @@ class PagedAttention(Mixer):
         if spec.gate_weight:
             wanted[spec.gate_weight] = TensorRequest((ctx_dim if spec.gate_per_element else spec.num_heads,
                                                       spec.hidden_size))
+        if getattr(spec, "q_norm_weight", None):
+            wanted[spec.q_norm_weight] = TensorRequest((q_dim,), "around_one")
+        if getattr(spec, "k_norm_weight", None) and not spec.shares_kv:
+            wanted[spec.k_norm_weight] = TensorRequest((kv_dim,), "around_one")
         return wanted
 
     @classmethod
@@ -155,6 +159,15 @@ class PagedAttention(Mixer):
             self.w_o = torch.cat([self.w_o, self.w_o.new_zeros(s.hidden_size, self.ctx_width - self.ctx_dim)], dim=1).contiguous()
         as_float = lambda name: self.rt.upload(tensors[name], torch.float32) if name else None
         self.q_bias, self.k_bias, self.v_bias = as_float(s.q_bias), as_float(s.k_bias), as_float(s.v_bias)
+        # a norm over a whole projection (all heads together) runs right after the projection and adds that
+        # projection's bias itself; the kernels behind it then see rows that need neither
+        self.norm_segments = []
+        if getattr(s, "q_norm_weight", None):
+            self.norm_segments.append((0, self.q_dim, self.q_bias, as_float(s.q_norm_weight)))
+            self.q_bias = None
+        if getattr(s, "k_norm_weight", None) and not s.shares_kv:
+            self.norm_segments.append((self.q_dim, self.kv_dim, self.k_bias, as_float(s.k_norm_weight)))
+            self.k_bias = None
         self.r1 = as_float(s.distance_bias.r1) if s.distance_bias else None
         self.r2 = as_float(s.distance_bias.r2) if s.distance_bias else None
         self.bias_table = None
@@ -186,6 +199,8 @@ class PagedAttention(Mixer):
         n = h.shape[0]
         fused = rt.workspace.get("qkv", (n, self.fused_width), torch.float32)
         ops.linear(h, self.w_qkv, fused, _ops.MODE_STORE_F32)
+        if self.norm_segments:
+            ops.projection_norm(fused, s.projection_norm_eps, self.norm_segments)
         k_cache, v_cache = step.cache.entry_kv(cache_entry)
         table = step.block_tables[step.cache.entry_group_index(cache_entry)]
         if step.is_decode and self._specialised():

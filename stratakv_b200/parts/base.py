@@ -23,7 +23,8 @@ import torch
 class TensorRequest:
     """A checkpoint tensor a part needs.  ``init`` tells the random-weights mode
     how to fill it: ``normal`` is N(0, std), ``around_one`` is 1 + N(0, std), ``positive`` is
-    0.05 + |N(0, 0.5)|, ``around_identity`` the identity matrix + N(0, std)."""
+    0.05 + |N(0, 0.5)|, ``around_identity`` the identity matrix + N(0, std), ``conv_taps`` N(0, 1) / taps,
+    ``unit_interval`` sigmoid(N(0, 1)), ``decay_logit`` N(-3, 1.5), ``half_normal`` |N(0, 0.5)|."""
     shape: Tuple[int, ...]
     init: str = "normal"
 
@@ -169,6 +170,11 @@ class Norm(Part):
 
 class Mixer(Part):
     role = "mixer"
+    # True if the mixer finds its per-sequence state ``state_offset`` floats into its cache entry's state rows (an
+    # attribute, 0 by default), so that a mixer which holds two mixers on one cache entry can place both states.
+    honours_state_offset = False
+    # True if the mixer multiplies its result by its attribute ``out_scale`` before it joins the stream.
+    scales_output = False
 
     @classmethod
     def cache_request(cls, spec) -> CacheRequest:

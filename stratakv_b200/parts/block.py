@@ -220,7 +220,31 @@ def multi_stream(layer: Layer, step, x, entry) -> None:
         stats.invalidate()
 
 
+def parallel_pair(layer: Layer, step, x, entry) -> None:
+    """``x += mixer(norm1(x)) + ffn(norm2(x))``: two norms of the same x, one for each branch, and then the layer's
+    ``token_input`` if it has one.  A layer may have no feed-forward (then it has no second norm either)."""
+    if layer.mixer_norm is None or layer.mixer is None:
+        raise ValueError("the parallel_pair arrangement needs a norm and a mixer")
+    if layer.ffn is not None and layer.ffn_norm is None:
+        raise ValueError("the parallel_pair arrangement needs a norm of its own for the feed-forward")
+    stats = step.residual_stats
+    if stats is not None:
+        stats.expect(None)                          # nothing here folds a norm into a projection
+    # both norms read the stream before either branch has been added to it
+    h_mixer = layer.mixer_norm.forward(x, name="normed")
+    h_ffn = layer.ffn_norm.forward(x, name="normed_second") if layer.ffn is not None else None
+    layer.mixer.forward(step, h_mixer, x, entry.cache, entry.writes_cache)
+    if layer.ffn is not None:
+        layer.ffn.forward(step, h_ffn, x)
+    side = layer.extra.get("token_input")
+    if side is not None:
+        side.forward(step, x)
+    if stats is not None:
+        stats.invalidate()
+
+
 register_arrangement("multi_stream", multi_stream)
+register_arrangement("parallel_pair", parallel_pair)
 register_arrangement("pre_norm", pre_norm)
 register_arrangement("sandwich", sandwich)
 register_arrangement("parallel", parallel)

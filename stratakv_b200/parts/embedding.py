@@ -33,7 +33,13 @@ class TokenEmbedding(Part):
     def forward(self, step, x, flags, stats=None) -> None:
         """Fill the stream ``x`` [tokens, hidden] for ``step.token_ids``; an id outside the table raises
         bit 0 of ``flags``.  ``stats``: see ``residual.ResidualStats`` (the kernel fills it where it can)."""
-        self.rt.kernels().embed(self.table, step.token_ids, x, flags, stats=stats)
+        scale = getattr(self.spec, "scale", 1.0)
+        # (a scaled row is not what the folded norm's statistics were taken of: the norm then runs as a kernel)
+        self.rt.kernels().embed(self.table, step.token_ids, x, flags, stats=stats if scale == 1.0 else None)
+        if scale != 1.0:
+            self.rt.kernels().scale_inplace(x, scale)
+            if stats is not None:
+                stats.invalidate()
 
 
 class SummedEmbedding(Part):

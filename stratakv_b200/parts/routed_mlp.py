@@ -1,11 +1,15 @@
 """A mixture of experts: every token runs through the ``top`` experts that its router scores choose, and through a
 shared expert if the layer has one.
 
-    s = sigmoid(router h)                       float32, one score per expert
-    chosen: the `top` largest s + correction    (the correction chooses only)
+    s = sigmoid(router h)                       float32, one score per expert (spec.score "softmax": a softmax over them)
+    chosen: the `top` largest s + correction    (the correction chooses only; with spec.groups only experts of the
+                                                 keep_groups best groups, a group scoring what its best expert does)
     y = sum over chosen e of s_e * route_scale * down_e act(up_e h)          (weights divided by their sum first if
                                                                                the spec says `renormalize`)
       + sigmoid(shared.gate . h) * shared.down act(shared.up h)
+
+An expert may be gated (``spec.gate_weights``): ``down_e (act(gate_e h) * (up_e h))``, gate and up rows packed in tiles as
+the dense gated feed-forward packs them.
 
 Kernels (``csrc/routed_mlp.cu``): the router (scores, choice, weights, the shared expert's gate), a counting sort of
 the (token, expert) pairs by expert, the two projections over the sorted pairs (each block of rows reads the
@@ -19,6 +23,7 @@ import torch
 
 from .. import ops as _ops
 from .base import FeedForward, TensorRequest
+from .ffn import pack_gate_up
 from .registry import register_ffn
 
 
@@ -35,6 +40,16 @@ class RoutedMlp(FeedForward):
                              f"{_ops.MAX_EXPERTS_PER_TOKEN} of {_ops.MAX_EXPERTS})")
         if len(spec.up_weights) != spec.experts or len(spec.down_weights) != spec.experts:
             raise ValueError("routed feed-forward: one pair of tensor names per expert is needed")
+        self.gated = getattr(spec, "gate_weights", None) is not None
+        if self.gated and len(spec.gate_weights) != spec.experts:
+            raise ValueError("routed feed-forward: one gate tensor per expert is needed")
+        self.score = getattr(spec, "score", "sigmoid")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"routed feed-forward: scores '{self.score}' are not supported (sigmoid, softmax)")
+        self.groups, self.keep = getattr(spec, "groups", 0), getattr(spec, "keep_groups", 0)
+        if self.groups > 1 and (spec.experts % self.groups or not 0 < self.keep <= self.groups
+                                or self.keep * (spec.experts // self.groups) < spec.top):
+            raise ValueError("routed feed-forward: the groups must divide the experts and the kept ones hold the choices")
         if runtime.dtype == torch.bfloat16 and spec.hidden_size % 8 != 0:
             raise ValueError(f"routed feed-forward: hidden size {spec.hidden_size} is not supported in bfloat16 "
                              "(rows of 16 bytes are needed: a multiple of 8); float32 takes any size")
@@ -49,6 +64,8 @@ class RoutedMlp(FeedForward):
         for up, down in zip(spec.up_weights, spec.down_weights):
             wanted[up] = TensorRequest((spec.intermediate_size, spec.hidden_size))
             wanted[down] = TensorRequest((spec.hidden_size, spec.intermediate_size))
+        for gate in getattr(spec, "gate_weights", None) or ():
+            wanted[gate] = TensorRequest((spec.intermediate_size, spec.hidden_size))
         if spec.shared is not None:
             wanted[spec.shared.up_weight] = TensorRequest((spec.shared.intermediate_size, spec.hidden_size))
             wanted[spec.shared.down_weight] = TensorRequest((spec.hidden_size, spec.shared.intermediate_size))
@@ -71,8 +88,10 @@ class RoutedMlp(FeedForward):
         self.correction = (rt.upload(tensors[s.correction], torch.float32).reshape(-1).contiguous()
                            if s.correction is not None else None)
         ups, downs = [], []
-        for up_name, down_name in zip(s.up_weights, s.down_weights):
+        for index, (up_name, down_name) in enumerate(zip(s.up_weights, s.down_weights)):
             up, down = self._padded(rt.upload(tensors[up_name]), rt.upload(tensors[down_name]), self.padded)
+            if self.gated:                          # [2 ff, hidden]: tiles of 8 gate rows and their 8 up rows
+                up = pack_gate_up(rt.upload(tensors[s.gate_weights[index]]), up[:s.intermediate_size])
             ups.append(up)
             downs.append(down)
         self.w_up = torch.stack(ups).contiguous()            # [experts, ff, hidden]
@@ -94,7 +113,8 @@ class RoutedMlp(FeedForward):
         weights = get("routed_weights", (n, s.top), torch.float32)
         share = get("routed_share", (n,), torch.float32) if self.shared_gate is not None else None
         ops.route_tokens(h, self.w_router, self.correction, s.top, s.route_scale, s.renormalize, chosen, weights,
-                         shared_gate_weight=self.shared_gate, shared_gate_out=share)
+                         shared_gate_weight=self.shared_gate, shared_gate_out=share, softmax=self.score == "softmax",
+                         groups=self.groups, keep=self.keep, renorm_eps=getattr(s, "renormalize_eps", 0.0))
         if step.choice_probe is not None:
             step.choice_probe(step.run_index, step, chosen)
         offsets = get("routed_offsets", (s.experts + 1,), torch.int32)
@@ -106,9 +126,9 @@ class RoutedMlp(FeedForward):
             # the tensor-core projection reads tiles of neighbouring rows: bring the tokens' rows into sorted order first
             gathered = get("routed_rows", (pairs, s.hidden_size), rt.dtype)
             ops.gather_rows(h, order, gathered)
-            ops.expert_linear(gathered, self.w_up, offsets, hidden, activation=s.activation)
+            ops.expert_linear(gathered, self.w_up, offsets, hidden, activation=s.activation, gated=self.gated)
         else:
-            ops.expert_linear(h, self.w_up, offsets, hidden, rows=order, activation=s.activation)
+            ops.expert_linear(h, self.w_up, offsets, hidden, rows=order, activation=s.activation, gated=self.gated)
         results = get("routed_results", (pairs, s.hidden_size), torch.float32)
         ops.expert_linear(hidden, self.w_down, offsets, results)
         shared_out = None

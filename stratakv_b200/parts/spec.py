@@ -49,11 +49,13 @@ class YarnSpec:
 class RotarySpec:
     """Rotary positions on the first ``dims`` numbers of a vector (the rest pass), number i paired with number
     ``i + dims/2``: ``(u, v) -> (u cos a - v sin a, v cos a + u sin a)``, ``a = position * base^(-2i/dims)``;
-    ``scaling`` changes the frequencies (``YarnSpec``)."""
+    ``scaling`` changes the frequencies (``YarnSpec``).  ``interleaved``: pair i is numbers ``2i`` and ``2i + 1``
+    instead (mixers whose kernels know both layouts read it; the table is the same)."""
     dims: int
     base: float
     scaling: Optional[YarnSpec] = None
     kind: str = "rotary_table"
+    interleaved: bool = False
 
 
 @dataclass(frozen=True)
@@ -87,7 +89,9 @@ class AttentionSpec:
     cached.  ``q_temperature``: see ``QueryTemperatureSpec``.  ``softcap`` c > 0: scores become
     ``c * tanh(score / c)`` before the softmax.  ``shares_kv``: the mixer has no key and value projections and
     attends over the cache entry that another layer's run wrote (its schedule entry names that entry and does
-    not write it)."""
+    not write it).  ``q_norm_weight`` / ``k_norm_weight`` (tensor names, ``[heads * head_dim]`` and
+    ``[kv_heads * head_dim]``) with ``projection_norm_eps``: one RMS norm with that weight over ALL query heads
+    together, and one over all key heads, after the biases and before the heads are split."""
     hidden_size: int
     num_heads: int
     num_kv_heads: int
@@ -112,6 +116,9 @@ class AttentionSpec:
     q_temperature: Optional[QueryTemperatureSpec] = None
     softcap: float = 0.0
     shares_kv: bool = False
+    q_norm_weight: Optional[str] = None
+    k_norm_weight: Optional[str] = None
+    projection_norm_eps: float = 0.0
 
     @property
     def value_dim(self) -> int:
@@ -122,7 +129,8 @@ class AttentionSpec:
         """True if any mechanism beyond rotated, unbiased queries, keys and values of one width is in use."""
         return bool(self.v_head_dim and self.v_head_dim != self.head_dim or self.q_bias or self.k_bias
                     or self.v_bias or self.value_norm_eps is not None or self.distance_bias or self.gate_weight
-                    or self.qk_norm_eps is not None or self.q_temperature or self.softcap or self.shares_kv)
+                    or self.qk_norm_eps is not None or self.q_temperature or self.softcap or self.shares_kv
+                    or self.q_norm_weight or self.k_norm_weight)
 
 
 @dataclass(frozen=True)
@@ -180,6 +188,74 @@ class RetentionSpec:
     gate_weight: str                 # [heads * v_head_dim, hidden]
     o_weight: str                    # [hidden, heads * v_head_dim]
     kind: str = "retention"
+
+
+@dataclass(frozen=True)
+class ConvAttentionSpec:
+    """Causal grouped-query attention whose queries and keys pass a short convolution over time before they are
+    rotated: ``q, k = conv(Wq h + bq), conv(Wk h + bk)`` with ``conv(u)_p = sum_j w[:, j] u_(p - taps + 1 + j)`` per
+    channel (zeros before the sequence; the biased projections of the last ``taps - 1`` positions are state a sequence
+    keeps); rotary positions (``rope``) on queries and keys; ``values_are_keys``: there is no value projection and the
+    values are the convolved keys before rotation; ``score = (q . k) scale`` over the last ``window`` keys (0: all);
+    ``sink``: a learned number per head whose exponential counts once in the softmax's denominator; ``Wo`` on the
+    heads.  ``taps`` 0: no convolution."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    scale: float
+    q_weight: str                    # [heads * head_dim, hidden]
+    k_weight: str                    # [kv_heads * head_dim, hidden]
+    o_weight: str                    # [hidden, heads * head_dim]
+    taps: int = 0
+    q_conv: Optional[str] = None     # [heads * head_dim, taps], the last column weighs the current token
+    k_conv: Optional[str] = None     # [kv_heads * head_dim, taps]
+    q_bias: Optional[str] = None
+    k_bias: Optional[str] = None
+    rope: Optional[RotarySpec] = None
+    window: int = 0
+    sink: Optional[str] = None       # [heads]
+    values_are_keys: bool = True
+    kind: str = "conv_attention"
+
+
+@dataclass(frozen=True)
+class TimeMixSpec:
+    """Time mixing with a matrix state per head and a decay per token and key channel (the RWKV family).  With h' the
+    token before's input (zeros for the first), every projection s of r, k, v, g, w reads ``h + (h' - h) mu_s``;
+    ``r, k, v = Wr., Wk., Wv.`` (heads x head_dim), ``gate = silu(Wg.)``, ``w = exp(-exp(W2 tanh(W1 .) + w0))`` per head
+    and key channel; per head ``o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t`` and ``S_t = diag(w_t) S_(t-1) + k_t v_t^T``
+    (S float32, zero before the first token); every head of o divided by its root mean square (``eps``), times
+    ``norm``, times the gate, then ``Wo``."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    decay_rank: int
+    eps: float
+    mix: Tuple[str, str, str, str, str]   # the mu tensors of r, k, v, g, w, each [hidden]
+    r_weight: str                    # [heads * head_dim, hidden]
+    k_weight: str
+    v_weight: str
+    g_weight: str
+    w1_weight: str                   # [decay_rank, hidden]
+    w2_weight: str                   # [heads * head_dim, decay_rank]
+    w0: str                          # [heads * head_dim]
+    bonus: str                       # u, [heads, head_dim]
+    norm: str                        # [heads * head_dim]
+    o_weight: str                    # [hidden, heads * head_dim]
+    kind: str = "time_mix"
+
+
+@dataclass(frozen=True)
+class MixerPairSpec:
+    """Two mixers side by side on the same input: ``left_scale * left(h) + right_scale * right(h)``.  Either side is
+    any mixer's spec; one cache entry serves both (the left one's pages, and both sides' per-sequence state one after
+    the other)."""
+    left: Any
+    right: Any
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "mixer_pair"
 
 
 @dataclass(frozen=True)
@@ -277,6 +353,14 @@ class RoutedMlpSpec:
     renormalize: bool = False
     shared: Optional[SharedExpertSpec] = None
     kind: str = "routed_mlp"
+    # gated experts: ``down_e (act(gate_e h) * (up_e h))``, one more tensor per expert
+    gate_weights: Optional[Tuple[str, ...]] = None
+    score: str = "sigmoid"           # or "softmax": the scores are a softmax over all experts
+    # the experts form ``groups`` equal groups of neighbours; a group scores what its best expert does, and only
+    # experts of the ``keep_groups`` best groups can be chosen (0: no groups)
+    groups: int = 0
+    keep_groups: int = 0
+    renormalize_eps: float = 0.0     # added to the chosen scores' sum before ``renormalize`` divides by it
 
 
 @dataclass(frozen=True)
@@ -304,6 +388,8 @@ class LayerSpec:
     its two norms) may be ``None``.
     ``multi_stream``: the ``pre_norm`` block over several copies of the stream; the extras ``mixer_streams`` and
     ``ffn_streams`` (``StreamMixSpec``) say how each sublayer reads and writes them; ``ffn`` may be ``None``.
+    ``parallel_pair``: ``x += mixer(norm1(x)) + ffn(norm2(x))``, both norms of the same x, then ``token_input`` if the
+    layer has one; ``ffn`` (with its norm) may be ``None``.
 
     The four named places are what that arrangement uses; another arrangement may leave
     some of them ``None`` (a block without a feed-forward, one norm for two branches) and
@@ -327,10 +413,13 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``cache`` is the index of the cache entry the run's
-    mixer uses; ``writes_cache`` false means it only reads what another run wrote."""
+    mixer uses; ``writes_cache`` false means it only reads what another run wrote.
+    ``adds_embedding``: the embedding's output is added to the stream once more right before this run (a model that
+    runs some of its layers several times in a row feeds its input to every pass)."""
     layer: int
     cache: int
     writes_cache: bool = True
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -339,6 +428,7 @@ class EmbeddingSpec:
     hidden_size: int
     weight: str
     kind: str = "embedding"
+    scale: float = 1.0               # the table's rows times this
 
 
 @dataclass(frozen=True)

@@ -80,6 +80,11 @@ def read_checkpoint(model_dir) -> Dict[str, torch.Tensor]:
     return tensors
 
 
+def tensor_shapes(model_dir) -> Dict[str, Tuple[int, ...]]:
+    """Name -> shape of every tensor of the checkpoint (its headers only are read)."""
+    return {name: tuple(tensor.shape) for name, tensor in read_checkpoint(model_dir).items()}
+
+
 def check_and_select(source, tensors: Mapping[str, torch.Tensor],
                      expected: Mapping[str, Tuple[int, ...]],
                      ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:

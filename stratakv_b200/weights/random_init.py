@@ -35,6 +35,14 @@ def random_tensor(name: str, request: TensorRequest, seed: int, std: float,
         values = values.abs() / std * 0.5 + 0.05
     elif request.init == "around_identity":    # a square matrix that mixes a little
         values += torch.eye(request.shape[0], request.shape[1], device=device)
+    elif request.init == "conv_taps":          # [channels, taps] of a short convolution: taps of order 1 / taps
+        values = values / std / max(1, request.shape[-1])
+    elif request.init == "unit_interval":      # factors between 0 and 1 (how much of the token before a mix takes)
+        values = torch.sigmoid(values / std)
+    elif request.init == "decay_logit":        # w0 of a decay exp(-exp(w0)): decays from 0.37 (fast) to 0.998 (slow)
+        values = values / std * 1.5 - 3.0
+    elif request.init == "half_normal":        # non-negative numbers of order one half
+        values = values.abs() / std * 0.5
     elif request.init != "normal":
         raise ValueError(f"unknown init '{request.init}' for tensor {name}")
     return values.to(dtype)

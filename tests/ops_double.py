@@ -289,14 +289,20 @@ class DoubleKernels:
             cache[block, 0, pos % block_size, :] = rows[t].to(cache.dtype)
 
     def route_tokens(self, h, router_w, correction, top, scale, renormalize, chosen, weights, shared_gate_weight=None,
-                     shared_gate_out=None):
+                     shared_gate_out=None, softmax=False, groups=0, keep=0, renorm_eps=0.0):
         self.calls.append("route_tokens")
-        s = torch.sigmoid(h.float() @ router_w.float().T)
+        logits = h.float() @ router_w.float().T
+        s = torch.softmax(logits, dim=-1) if softmax else torch.sigmoid(logits)
         choice = s + correction if correction is not None else s
+        if groups > 1:
+            size = s.shape[1] // groups
+            best = choice.view(-1, groups, size).max(dim=-1).values
+            kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, best.topk(keep, dim=-1).indices, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(size, dim=1), -float("inf"))
         picked = torch.topk(choice, top, dim=-1).indices
         w = torch.gather(s, 1, picked)
         if renormalize:
-            w = w / w.sum(dim=-1, keepdim=True)
+            w = w / (w.sum(dim=-1, keepdim=True) + renorm_eps)
         chosen.copy_(picked.to(torch.int32))
         weights.copy_(w * scale)
         if shared_gate_out is not None:
@@ -315,7 +321,7 @@ class DoubleKernels:
     def expert_rows_sorted_first(self, hidden):
         return False
 
-    def expert_linear(self, a, w, offsets, out, rows=None, activation=None, flag=None):
+    def expert_linear(self, a, w, offsets, out, rows=None, activation=None, flag=None, gated=False):
         self.calls.append("expert_linear")
         for e in range(w.shape[0]):
             lo, hi = int(offsets[e]), int(offsets[e + 1])
@@ -323,7 +329,10 @@ class DoubleKernels:
                 continue
             src = a[rows[lo:hi].long()] if rows is not None else a[lo:hi]
             result = src.float() @ w[e].float().T
-            if activation is not None:
+            if gated:                               # tiles of 8 gate rows and their 8 up rows
+                tiles = result.view(result.shape[0], -1, 2, 8)
+                result = (ACTIVATIONS[activation](tiles[:, :, 0]) * tiles[:, :, 1]).reshape(result.shape[0], -1)
+            elif activation is not None:
                 result = ACTIVATIONS[activation](result)
             out[lo:hi] = result.to(out.dtype)
 
