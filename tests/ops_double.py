@@ -401,6 +401,121 @@ class DoubleKernels:
             for back in range(min(taps, last - first + 1)):
                 ring[(p_last - back) % taps] = yx[last - back, x_offset:x_offset + channels] + x_bias
 
+    def add_scaled(self, out, other, factor):
+        self.calls.append("add_scaled")
+        out.add_(other * factor)
+
+    def projection_norm(self, rows, eps, segments):
+        self.calls.append("projection_norm")
+        for offset, width, bias, weight in segments:
+            x = rows[:, offset:offset + width] + (bias if bias is not None else 0.0)
+            rows[:, offset:offset + width] = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * weight
+
+    def short_conv_rotary(self, rows, bias, conv_w, taps, cos_sin, rotated, interleaved, block_table, q_out, k_cache,
+                          v_cache, num_heads, num_kv_heads, dim, block_size, write_kv, step_meta, state, state_offset=0):
+        self.calls.append("short_conv_rotary")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        n, channels = rows.shape[0], (num_heads + num_kv_heads) * dim
+        u = rows[:, :channels] + (bias if bias is not None else 0.0)
+        y = torch.zeros(n, channels)
+        for t in range(n):
+            seq, p = int(token_seq[t]), int(positions[t])
+            first = int(cu_q[seq])
+            if taps == 0:
+                y[t] = u[t]
+                continue
+            ring = (state[int(slot_ids[seq])][state_offset:state_offset + taps * channels].view(taps, channels)
+                    if taps > 1 else None)
+            for j in range(taps):
+                back = taps - 1 - j
+                if p - back >= 0:
+                    y[t] += conv_w[:, j] * (u[t - back] if t - back >= first else ring[(p - back) % taps])
+        heads = y.view(n, num_heads + num_kv_heads, dim)
+        turned = heads.clone()
+        if rotated:
+            cs = cos_sin[positions.long()]                            # [n, rotated / 2, 2]
+            c, sn = cs[:, None, :, 0], cs[:, None, :, 1]
+            if interleaved:
+                a, b = heads[..., 0:rotated:2], heads[..., 1:rotated:2]
+                turned[..., 0:rotated:2], turned[..., 1:rotated:2] = a * c - b * sn, b * c + a * sn
+            else:
+                half = rotated // 2
+                a, b = heads[..., :half], heads[..., half:rotated]
+                turned[..., :half], turned[..., half:rotated] = a * c - b * sn, b * c + a * sn
+        q_out.copy_(turned[:, :num_heads].reshape(n, num_heads * dim).to(q_out.dtype))
+        if not write_kv:
+            return
+        for t in range(n):
+            pos = int(positions[t])
+            block = int(block_table[int(token_seq[t]), pos // block_size])
+            k_cache[block, :, pos % block_size, :] = turned[t, num_heads:].to(k_cache.dtype)
+            if v_cache is not None:
+                v_cache[block, :, pos % block_size, :] = heads[t, num_heads:].to(v_cache.dtype)
+
+    def short_conv_remember(self, rows, bias, channels, taps, n_seqs, step_meta, state, state_offset=0):
+        self.calls.append("short_conv_remember")
+        if taps <= 1:
+            return
+        positions, token_seq, cu_q, slot_ids = step_meta
+        for seq in range(n_seqs):
+            first, end = int(cu_q[seq]), int(cu_q[seq + 1])
+            ring = state[int(slot_ids[seq])][state_offset:state_offset + taps * channels].view(taps, channels)
+            for t in range(max(first, end - (taps - 1)), end):
+                ring[int(positions[t]) % taps] = rows[t, :channels] + (bias if bias is not None else 0.0)
+
+    def time_mix_state_floats(self, hidden, heads, dim):
+        return 2 * heads * dim * dim + 2 * hidden
+
+    def token_shift_mix(self, h, mu, mixes, heads, dim, step_meta, state, state_offset=0):
+        self.calls.append("token_shift_mix")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        hidden = h.shape[1]
+        base = state_offset + 2 * heads * dim * dim
+        for t in range(h.shape[0]):
+            seq, p = int(token_seq[t]), int(positions[t])
+            if t > int(cu_q[seq]):
+                before = h[t - 1].float()
+            elif p > 0:
+                before = state[int(slot_ids[seq])][base + ((p - 1) & 1) * hidden:][:hidden]
+            else:
+                before = torch.zeros(hidden)
+            now = h[t].float()
+            for m in range(mixes.shape[0]):
+                mixes[m, t] = (now + (before - now) * mu[m]).to(mixes.dtype)
+
+    def time_mix_decay(self, lora, rank, w2, w0, decay):
+        self.calls.append("time_mix_decay")
+        decay.copy_(torch.exp(-torch.exp(torch.tanh(lora[:, :rank]) @ w2.float().T + w0)))
+
+    def time_mix_scan(self, r, k, v, decay, bonus, out, h, n_seqs, heads, dim, step_meta, state, state_offset=0):
+        self.calls.append("time_mix_scan")
+        positions, token_seq, cu_q, slot_ids = step_meta
+        hidden, size = h.shape[1], heads * dim * dim
+        u = bonus.view(heads, dim)
+        for seq in range(n_seqs):
+            first, end = int(cu_q[seq]), int(cu_q[seq + 1])
+            if end <= first:
+                continue
+            row = state[int(slot_ids[seq])]
+            p0 = int(positions[first])
+            S = (row[state_offset + ((p0 - 1) & 1) * size:][:size].clone().view(heads, dim, dim) if p0 > 0
+                 else torch.zeros(heads, dim, dim))
+            for t in range(first, end):
+                kv = k[t].view(heads, dim)[:, :, None] * v[t].view(heads, dim)[:, None, :]
+                out[t] = torch.einsum("hi,hij->hj", r[t].view(heads, dim), S + u[:, :, None] * kv).reshape(-1)
+                S = decay[t].view(heads, dim)[:, :, None] * S + kv
+            last = p0 + end - first - 1
+            row[state_offset + (last & 1) * size:][:size] = S.reshape(size)
+            row[state_offset + 2 * size + (last & 1) * hidden:][:hidden] = h[end - 1].float()
+
+    def time_mix_finish(self, o, gate, norm, eps, out_scale, out, heads, dim):
+        self.calls.append("time_mix_finish")
+        n = o.shape[0]
+        heads_o = o.view(n, heads, dim)
+        unit = heads_o / torch.sqrt((heads_o * heads_o).mean(dim=-1, keepdim=True) + eps)
+        out.zero_()
+        out[:, :heads * dim] = (unit.reshape(n, -1) * norm * gate * torch.sigmoid(gate) * out_scale).to(out.dtype)
+
     def scale_inplace(self, x, factor):
         x.mul_(factor)
 

@@ -192,7 +192,15 @@ def dense_ff(h, P, p, mlp):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ P[p + "down"].T
 
 
-def route(h, P, p, router):
+# Where the engine computes in bfloat16 its router sees a rounded input, and where two experts (or two groups) score
+# nearly alike it may choose the other one: that is no fault.  ``proposed`` ([T, top] expert indices, -1 where unknown)
+# is the engine's choice; it is followed where its experts score at least CLOSE_CALL of what the plain choice's do,
+# and counted in FAR_CALLS otherwise (DECISIONS counts all choices that were compared).
+CLOSE_CALL = 0.85
+FAR_CALLS, DECISIONS = [], [0]
+
+
+def route(h, P, p, router, proposed=None):
     """Per token: the chosen experts and their weights."""
     E, top = router["experts"], router["top"]
     s = torch.softmax(h @ P[p + "router"].T, dim=-1)
@@ -205,6 +213,17 @@ def route(h, P, p, router):
         allowed = torch.zeros(s.shape[0], groups["count"], dtype=torch.bool).scatter_(1, kept, True)
         allowed = allowed.repeat_interleave(size, dim=1)
     chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
+    if proposed is not None:
+        for t in range(s.shape[0]):
+            theirs = proposed[t]
+            if int(theirs.min()) < 0 or set(theirs.tolist()) == set(chosen[t].tolist()):
+                continue
+            DECISIONS[0] += 1
+            if float(s[t, theirs].sum()) >= CLOSE_CALL * float(s[t, chosen[t]].sum()):
+                chosen[t] = theirs
+            else:
+                FAR_CALLS.append((p, t))
+        DECISIONS[0] += s.shape[0]
     weights = s.gather(1, chosen)
     return chosen, weights / (weights.sum(dim=-1, keepdim=True) + 1e-20)
 
@@ -213,8 +232,8 @@ def expert(h, P, p):
     return (silu(h @ P[p + "gate"].T) * (h @ P[p + "up"].T)) @ P[p + "down"].T
 
 
-def moe(h, P, p, mlp):
-    chosen, weights = route(h, P, p, mlp["router"])
+def moe(h, P, p, mlp, proposed=None):
+    chosen, weights = route(h, P, p, mlp["router"], proposed)
     y = torch.zeros(h.shape[0], P[p + "e0.down"].shape[0], dtype=F64)
     for t in range(h.shape[0]):
         for e, w in zip(chosen[t].tolist(), weights[t]):
@@ -222,8 +241,8 @@ def moe(h, P, p, mlp):
     return y
 
 
-def feed_forward(h, P, p, mlp):
-    return dense_ff(h, P, p, mlp) if mlp["kind"] == "dense" else moe(h, P, p, mlp)
+def feed_forward(h, P, p, mlp, proposed=None):
+    return dense_ff(h, P, p, mlp) if mlp["kind"] == "dense" else moe(h, P, p, mlp, proposed)
 
 
 # ---- the model ------------------------------------------------------------------------------------------------------
@@ -235,7 +254,7 @@ def token_side(x, tokens, P, i, dim, eps):
     return x + unit_rms(y, eps) * P[p + "norm"]
 
 
-def layer(x, tokens, cfg, P, i):
+def layer(x, tokens, cfg, P, i, proposed=None):
     spec, eps, p = cfg["layers"][i], cfg["norm"]["eps"], f"l{i}."
     h = norm(x, P[p + "norm1"], eps)
     if spec["type"] == "attention":
@@ -243,7 +262,7 @@ def layer(x, tokens, cfg, P, i):
     else:
         branch = parallel_mixer(h, P, p + "mix.", spec["mixer"], eps)
     if spec.get("mlp"):
-        branch = branch + feed_forward(norm(x, P[p + "norm2"], eps), P, p + "mlp.", spec["mlp"])
+        branch = branch + feed_forward(norm(x, P[p + "norm2"], eps), P, p + "mlp.", spec["mlp"], proposed)
     x = x + branch
     side = (cfg.get("token_side") or {}).get("dim", 0)
     return token_side(x, tokens, P, i, side, eps) if side else x
@@ -261,16 +280,17 @@ def layer_runs(cfg):
     return order + list(range(loop["stop"], n)), again
 
 
-def forward(cfg, P, tokens, layer_outputs=None):
-    """Logits [T, vocab] of one sequence; ``layer_outputs`` (a list) gets the stream after every run of a layer."""
+def forward(cfg, P, tokens, layer_outputs=None, proposed=None):
+    """Logits [T, vocab] of one sequence; ``layer_outputs`` (a list) gets the stream after every run of a layer;
+    ``proposed``: run index -> the experts another implementation chose there (see ``route``)."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    first = P["embed"][tokens] * cfg["embedding"]["scale"]
+    first = P["embed"][tokens] * (cfg.get("embedding") or {}).get("scale", 1.0)
     x = first
     order, again = layer_runs(cfg)
     for run, i in enumerate(order):
         if run in again:
             x = x + first
-        x = layer(x, tokens, cfg, P, i)
+        x = layer(x, tokens, cfg, P, i, proposed.get(run) if proposed else None)
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return norm(x, P["final.norm"], cfg["norm"]["eps"]) @ P["head"].T
@@ -307,5 +327,5 @@ def load_folder(folder):
     return cfg, P
 
 
-def logits_of(cfg, P, tokens):
-    return forward(cfg, P, tokens).to(torch.float32).numpy()
+def logits_of(cfg, P, tokens, proposed=None):
+    return forward(cfg, P, tokens, proposed=proposed).to(torch.float32).numpy()
