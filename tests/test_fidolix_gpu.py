@@ -21,10 +21,11 @@ DTYPES = ["float32", "bfloat16"]
 # projection's inputs moves most positions by a few hundredths of the spread and a few by more; a lost sink, gate,
 # state, tap, window edge or group moves positions by 0.16 or more (tests/test_fidolix.py shows that on the plain
 # implementation).  So: ROW_NOISE for all but ROWS_OVER of a request's positions (one, in a short request), ROW_LIMIT
-# for every position, MEAN_NOISE for their root mean square; and the routers' choices may differ from the plain ones by
+# for every position (a router that chooses one expert of sixteen sharpened ones moves a position that far when it
+# makes a call that is not close enough to be followed), MEAN_NOISE for their root mean square; and the routers' choices may differ from the plain ones by
 # more than a close call in FAR_CALLS of the decisions (plus one).
 ROW_NOISE = {"bfloat16": 0.08, "float32": 1.5e-4}
-ROWS_OVER, ROW_LIMIT, MEAN_NOISE, FAR_CALLS = 0.04, 0.3, 0.05, 0.02
+ROWS_OVER, ROW_LIMIT, MEAN_NOISE, FAR_CALLS = 0.04, 0.45, 0.05, 0.02
 
 
 class Folders:
