@@ -4,6 +4,7 @@
     python bench.py --design zepavik [--layers 8]       (the Zepavik decoder beside Llama at equal layer sizes)
     python bench.py --design povusun [--layers 8]       (the Povusun decoder beside Llama: mixed layers, and each of its
                                                          three mixers alone)
+    python bench.py --design fidolix [--layers 8]       (the Fidolix decoder beside Llama and beside the Kedelorn decoder)
     python bench.py --design kedelorn [--layers 8]      (the Kedelorn decoder beside Llama and beside Povusun's latent and
                                                          recurrent layers: mixed layers, and each of its two mixers alone)
 
@@ -336,8 +337,98 @@ def kedelorn_arm(args) -> int:
     return 0
 
 
+def fidolix_config(size, layers, vocab, kinds, window=1024):
+    """A Fidolix configuration at a size of DESIGN_SIZES whose layer i has the mixer ``kinds[i % len(kinds)]``.  The
+    attention layers have Llama's heads, key heads and head size (values of the head size, a cap of 30).  A parallel
+    layer's left side has the same heads, four taps, the whole head rotated with stretched frequencies, a window of
+    ``window`` keys and a sink; its right side has Llama's heads and head size (as wide as the model inside) and a
+    decay of rank 64.  The first layer's feed-forward is dense with Llama's inner width; the others have eight gated
+    experts in two groups of which one is kept and two experts are chosen, each half as wide as Llama's, so that a token
+    passes through as many feed-forward weights as in Llama.  Every layer has a token input of 64 numbers.  No layer
+    runs twice (the arms have equal numbers of layer runs)."""
+    from stratakv_b200.config import FidolixConfig
+    d, heads, kv_heads = size["head_dim"], size["heads"], size["kv_heads"]
+    expert_ff = size["llama_ff"] // 2 // 64 * 64
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": 8, "top": 2, "groups": {"count": 2, "keep": 1}}}
+    made = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": size["llama_ff"], "limit": 7.0} if i == 0 else moe
+        if kinds[i % len(kinds)] == "attention":
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": d, "vdim": d, "scale": d ** -0.5, "softcap": 30.0}
+        else:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": d, "vdim": d, "conv": 4, "scale": d ** -0.5,
+                    "mask": {"size": window},
+                    "rot": {"dims": d, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+            mixer = {"left": left, "right": {"heads": heads, "dim": d, "rank": 64}, "left_scale": 0.8, "right_scale": 1.1}
+        made.append({"type": kinds[i % len(kinds)], "mixer": mixer, "mlp": mlp})
+    return FidolixConfig.from_dict({"architecture": "Fidolix", "vocab": vocab, "width": size["hidden"], "norm": {"eps": 1e-5},
+                                    "embedding": {"scale": 3.0}, "token_side": {"dim": 64}, "layers": made})
+
+
+def fidolix_arm(args) -> int:
+    """Prefill and decode of the Fidolix decoder beside the Llama decoder and beside the Kedelorn decoder (the
+    framework's nearest model: a recurrent mixer with a matrix state, attention with a sink, a routed feed-forward) at
+    equal layer sizes, random weights: a model that alternates its two kinds of layer, and one of each kind alone."""
+    import gc
+    import torch
+    from stratakv_b200.config import LlamaConfig
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    layers, vocab, context, batch = args.layers or 8, 32000, args.context, args.batch
+    steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    peak = peaks()
+    sizes = {}
+    sampler = ClockSampler()
+    sampler.start()
+    for name, size in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        window = args.window or 1024
+        configs = {"llama": LlamaConfig.from_dict(dict(
+            TINYLLAMA, hidden_size=size["hidden"], intermediate_size=size["llama_ff"], num_hidden_layers=layers,
+            num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"],
+            vocab_size=vocab, max_position_embeddings=context + 64)),
+            "kedelorn": kedelorn_config(size, layers, vocab, ("retention", "latent_attention")),
+            "kedelorn_retention_only": kedelorn_config(size, layers, vocab, ("retention",)),
+            "fidolix": fidolix_config(size, layers, vocab, ("attention", "parallel"), window),
+            "fidolix_attention_only": fidolix_config(size, layers, vocab, ("attention",), window),
+            "fidolix_parallel_only": fidolix_config(size, layers, vocab, ("parallel",), window)}
+        only = [label for label in args.arms.split(",") if label] if args.arms else list(configs)
+        row = {}
+        for label in only:
+            config = configs[label]
+            engine = engine_of(config, max(batch * (context + 64), PREFILL_TOKENS + 64), batch)
+            prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+            decode_ms, launches, _ = time_decode(engine, batch, context - steps - warmup, steps, warmup, vocab)
+            weight_bytes = engine.model.weight_bytes()
+            kv_bytes = batch * context * engine.cache.bytes_per_token()
+            row[label] = {"prefill_tokens_per_s": PREFILL_TOKENS * 1000.0 / prefill_ms, "prefill_ms": prefill_ms,
+                          "decode_tokens_per_s": batch * 1000.0 / decode_ms, "decode_ms_per_step": decode_ms,
+                          "decode_hbm_frac": (weight_bytes + kv_bytes) / (decode_ms * 1e-3) / 1e9 / peak["hbm_gbs"],
+                          "weight_bytes": weight_bytes, "cache_bytes_per_token": engine.cache.bytes_per_token(),
+                          "launches_in_timed_steps": launches}
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        if "llama" in row:
+            for label in row:
+                row[label]["prefill_ratio"] = row[label]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"]
+                row[label]["decode_ratio"] = row[label]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"]
+        sizes[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"design": "Fidolix", "beside": ["LlamaForCausalLM", "Kedelorn"], "layers": layers, "vocab": vocab,
+                      "prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "context": context, "dtype": "bf16",
+                      "steps": steps, "warmup": warmup,
+                      "data": "synthetic: random N(0,0.02) weights, uniform random token ids", "peaks": peak,
+                      "clocks": clocks, "sizes": sizes}))
+    return 0
+
+
 def design_arm(args) -> int:
     """Prefill and decode of the Zepavik decoder and of the Llama decoder at equal layer sizes (random weights)."""
+    if args.design == "fidolix":
+        return fidolix_arm(args)
     if args.design == "povusun":
         return povusun_arm(args)
     if args.design == "kedelorn":
@@ -691,10 +782,10 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the prefill")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context at which the timed decode steps end")
-    parser.add_argument("--design", choices=["zepavik", "povusun", "kedelorn"],
+    parser.add_argument("--design", choices=["zepavik", "povusun", "kedelorn", "fidolix"],
                         help="measure this design beside the Llama decoder at equal layer sizes instead of the step benchmark")
     parser.add_argument("--sizes", default="", help="with --design: names of DESIGN_SIZES, with commas (default: all)")
-    parser.add_argument("--arms", default="", help="with --design kedelorn: which models to time, with commas (default: all)")
+    parser.add_argument("--arms", default="", help="with --design kedelorn or fidolix: which models to time, with commas (default: all)")
     parser.add_argument("--window", type=int, default=0, help="with --design: the design's window (default: the whole context)")
     parser.add_argument("--workload", choices=sorted(WORKLOADS),
                         help="a whole generation workload through Engine.generate instead of the step benchmark")

@@ -1233,7 +1233,7 @@ static int launch_tc(const void* a, const void* w, void* out, int M, int N, int 
 // group's).  Blocks beyond the tiles there turn out to be leave at once.
 template <int BN, int STAGES>
 static int launch_grouped(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
-                          int groups, int N, int K, act_t act, int* flag, cudaStream_t stream) {
+                          int groups, int N, int K, act_t act, int gated, int* flag, cudaStream_t stream) {
     CUtensorMap map_a, map_w;
     if (int code = tensor_map(a, rows, K, 2, TC_BM, TC_BK, &map_a)) return code;
     if (int code = tensor_map(w, groups * N, K, 2, BN, TC_BK, &map_w)) return code;
@@ -1251,13 +1251,17 @@ static int launch_grouped(const void* a, const void* w, const int* offsets, void
     // no group leaves more than one part tile
     const long long tiles = ((long long)(rows + TC_BM - 1) / TC_BM + groups) * ((N + BN - 1) / BN);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-    const int mode = out_is_float ? TC_MODE_STORE_F32 : TC_MODE_STORE;
+    const int mode = gated ? TC_MODE_GATED : (out_is_float ? TC_MODE_STORE_F32 : TC_MODE_STORE);
     return launch_pdl("skv_expert_linear(tcgen05)", gemm_tcgen05_kernel<BN, STAGES>, grid, dim3(TC_THREADS), smem, stream,
                       map_a, map_w, map_a, 0, out, rows, N, K, mode, act, flag, RopeArgs{}, GroupArgs{offsets, groups});
 }
 
+// gated: every group's matrix holds N rows in tiles of 16 (8 gate rows, then their 8 up rows) and out is [rows, N / 2]
+// bfloat16, act(gate) * up; act is then the plain activation code.
 int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
-                           int groups, int N, int K, act_t act, int* flag, cudaStream_t stream) {
+                           int groups, int N, int K, act_t act, int gated, int* flag, cudaStream_t stream) {
+    if (gated && (N % 16 != 0 || out_is_float || (act & 0xff) == ACT_RELU2))
+        return fail("skv_expert_linear(tcgen05)", "a gated weight needs whole tiles of 16 rows, a bfloat16 result and a gate's activation");
     if (K % 8 != 0) return fail("skv_expert_linear(tcgen05)", "the inner size must be a multiple of 8 (16-byte rows)");
     if (((uintptr_t)a | (uintptr_t)w) & 15) return fail("skv_expert_linear(tcgen05)", "operands must be 16-byte aligned");
     if ((long long)groups * N > 0x7fffffffLL) return fail("skv_expert_linear(tcgen05)", "too many weight rows");
@@ -1266,8 +1270,8 @@ int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, voi
     // more blocks.
     const long long wide_tiles = ((long long)(rows + TC_BM - 1) / TC_BM + groups) * ((N + 255) / 256);
     if (N >= 256 && rows >= 2 * TC_BM * groups && wide_tiles >= tc_sm_count())
-        return launch_grouped<256, 4>(a, w, offsets, out, out_is_float, rows, groups, N, K, act, flag, stream);
-    return launch_grouped<128, 4>(a, w, offsets, out, out_is_float, rows, groups, N, K, act, flag, stream);
+        return launch_grouped<256, 4>(a, w, offsets, out, out_is_float, rows, groups, N, K, act, gated, flag, stream);
+    return launch_grouped<128, 4>(a, w, offsets, out, out_is_float, rows, groups, N, K, act, gated, flag, stream);
 }
 
 // The two-block form: clusters of two blocks, as many as the GPU runs at once (74 on 148 SMs), walk the 256 x 256 tiles.

@@ -357,7 +357,7 @@ combine_experts_kernel(const float* __restrict__ results, const int* __restrict_
 #if SKV_DTYPE == SKV_BF16
 // gemm_tcgen05.cu: the tensor-memory GEMM over rows sorted by group
 int grouped_linear_tcgen05(const void* a, const void* w, const int* offsets, void* out, int out_is_float, int rows,
-                           int groups, int N, int K, act_t act, int* flag, cudaStream_t stream);
+                           int groups, int N, int K, act_t act, int gated, int* flag, cudaStream_t stream);
 #endif
 
 }  // namespace skv
@@ -412,9 +412,11 @@ SKV_EXPORT int skv_expert_linear(const void* a, int a_stride, int a_rows, const 
     if (act >= ACT_SWIGLU_CLAMP) return fail("skv_expert_linear", "this activation is not served");
     if (gated && (act < 0 || N % 8 != 0)) return fail("skv_expert_linear", "a gated weight needs an activation and whole tiles of 8 rows");
 #if SKV_DTYPE == SKV_BF16
-    if (!gated && !rows && a_stride == K && K % 8 == 0 && a_rows >= pairs && !(((uintptr_t)a | (uintptr_t)w) & 15))
-        return grouped_linear_tcgen05(a, w, offsets, out, out_is_float, pairs, experts, N, K,
-                                      act >= 0 ? ((act_t)act | ACT_ON_STORE) : (act_t)0, flag, stream);
+    if (!rows && a_stride == K && K % 8 == 0 && a_rows >= pairs && !(((uintptr_t)a | (uintptr_t)w) & 15) &&
+        (!gated || (!out_is_float && act != ACT_RELU2)))
+        return grouped_linear_tcgen05(a, w, offsets, out, out_is_float, pairs, experts, gated ? 2 * N : N, K,
+                                      gated ? (act_t)act : (act >= 0 ? ((act_t)act | ACT_ON_STORE) : (act_t)0), gated,
+                                      flag, stream);
 #endif
     const int row_tiles = (pairs + EXP_ROWS - 1) / EXP_ROWS + experts;       // no expert leaves more than one part tile
     if (row_tiles > 65535) return fail("skv_expert_linear", "too many rows for one launch");

@@ -55,29 +55,48 @@ token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ mu, T*
     }
 }
 
-// decay[t][c] = exp(-exp(w0[c] + sum_j w2[c][j] * tanh(lora[t][j]))); a block per token.
+// decay[t][c] = exp(-exp(w0[c] + sum_j w2t[j][c] * tanh(lora[t][j]))); a block per TM_DECAY_TOKENS tokens, threads over
+// the channels (w2t is the weight transposed, [rank][channels], so that neighbouring threads read neighbouring numbers
+// and a number that is read serves all of the block's tokens).
+constexpr int TM_DECAY_TOKENS = 4;
 template <typename T>
 __global__ void __launch_bounds__(256)
-time_mix_decay_kernel(const float* __restrict__ lora, int lora_stride, int rank, const T* __restrict__ w2,
-                      const float* __restrict__ w0, float* __restrict__ decay, int channels) {
-    extern __shared__ __align__(16) float tm_lora[];
+time_mix_decay_kernel(const float* __restrict__ lora, int lora_stride, int rank, const T* __restrict__ w2t,
+                      const float* __restrict__ w0, float* __restrict__ decay, int n_tokens, int channels) {
+    extern __shared__ __align__(16) float tm_lora[];          // [TM_DECAY_TOKENS][rank]
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) tm_lora[j] = tanhf(lora[(size_t)t * lora_stride + j]);
+    const int t0 = blockIdx.x * TM_DECAY_TOKENS;
+    const int count = min(TM_DECAY_TOKENS, n_tokens - t0);
+    for (int idx = threadIdx.x; idx < TM_DECAY_TOKENS * rank; idx += blockDim.x) {
+        const int tok = idx / rank, j = idx - tok * rank;
+        tm_lora[idx] = tok < count ? tanhf(lora[(size_t)(t0 + tok) * lora_stride + j]) : 0.0f;
+    }
     __syncthreads();
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        const T* row = w2 + (size_t)c * rank;
-        float z = w0[c];
-        for (int j = 0; j < rank; ++j) z = fmaf(to_float(row[j]), tm_lora[j], z);
-        decay[(size_t)t * channels + c] = expf(-expf(z));
+        float z[TM_DECAY_TOKENS];
+#pragma unroll
+        for (int tok = 0; tok < TM_DECAY_TOKENS; ++tok) z[tok] = w0[c];
+        for (int j = 0; j < rank; ++j) {
+            const float w = to_float(w2t[(size_t)j * channels + c]);
+#pragma unroll
+            for (int tok = 0; tok < TM_DECAY_TOKENS; ++tok) z[tok] = fmaf(w, tm_lora[tok * rank + j], z[tok]);
+        }
+#pragma unroll
+        for (int tok = 0; tok < TM_DECAY_TOKENS; ++tok)
+            if (tok < count) decay[(size_t)(t0 + tok) * channels + c] = expf(-expf(z[tok]));
     }
 }
 
+__device__ __forceinline__ void tm_copy_async(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+
 // The recurrence.  A block per (sequence, head, slice of value columns); thread (column c, part s of `key_split`) keeps
-// S[i][c] for the key channels i = s, s + key_split, ...; the token's r, k, w (whole head) and v (the block's columns)
-// are staged in shared memory a few tokens at a time.  The head-0 block of a sequence's first slice also remembers the
-// mixer's input at the sequence's last token.
+// S[i][c] for the TM_REGS key channels i = s * TM_REGS ..; the tokens' r, k, w (the whole head, padded with zeros to
+// key_split * TM_REGS channels) and v (the block's columns) are staged in shared memory a few tokens at a time, the next
+// tokens' copies on their way while these are worked on.  The head-0 block of a sequence's first slice also remembers
+// the mixer's input at the sequence's last token.
 template <typename T>
 __global__ void __launch_bounds__(256)
 time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
@@ -97,55 +116,80 @@ time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, c
     float* s_write = slot_state + (size_t)((p0 + n - 1) & 1) * half + (size_t)head * dim * dim;
     const int part = threadIdx.x % key_split, c = threadIdx.x / key_split, col = col0 + c;
     const bool active = c < cols && col < dim;
+    const int padded = key_split * TM_REGS;
     float S[TM_REGS], u[TM_REGS];
 #pragma unroll
     for (int j = 0; j < TM_REGS; ++j) {
-        const int i = j * key_split + part;
+        const int i = part * TM_REGS + j;
         const bool held = active && i < dim;
         S[j] = held && p0 > 0 ? s_read[(size_t)i * dim + col] : 0.0f;
         u[j] = held ? bonus[(size_t)head * dim + i] : 0.0f;
     }
-    float* sr = tm_stage;                       // [chunk][dim]
-    float* sk = sr + (size_t)chunk * dim;
-    float* sw = sk + (size_t)chunk * dim;
-    float* sv = sw + (size_t)chunk * dim;       // [chunk][cols]
-    for (int t0 = 0; t0 < n; t0 += chunk) {
+    // two sets of buffers, each [chunk][padded] for r, k, w and [chunk][cols] for v
+    const int set = chunk * (3 * padded + cols);
+    for (int idx = threadIdx.x; idx < 2 * set; idx += blockDim.x) tm_stage[idx] = 0.0f;      // (the padding stays zero)
+    __syncthreads();
+
+    auto stage = [&](int which, int t0) {
+        float* sr = tm_stage + which * set;
+        float* sk = sr + chunk * padded;
+        float* sw = sk + chunk * padded;
+        float* sv = sw + chunk * padded;
         const int m = min(chunk, n - t0);
-        __syncthreads();
         for (int idx = threadIdx.x; idx < m * dim; idx += blockDim.x) {
             const int tok = idx / dim, i = idx - tok * dim;
             const size_t at = (size_t)(first + t0 + tok) * stride + (size_t)head * dim + i;
-            sr[idx] = r[at];
-            sk[idx] = k[at];
-            sw[idx] = decay[at];
+            tm_copy_async(sr + tok * padded + i, r + at);
+            tm_copy_async(sk + tok * padded + i, k + at);
+            tm_copy_async(sw + tok * padded + i, decay + at);
         }
-        for (int idx = threadIdx.x; idx < m * cols; idx += blockDim.x) {
-            const int tok = idx / cols, j = idx - tok * cols;
-            sv[idx] = col0 + j < dim ? v[(size_t)(first + t0 + tok) * stride + (size_t)head * dim + col0 + j] : 0.0f;
+        const int width = min(cols, dim - col0);
+        for (int idx = threadIdx.x; idx < m * width; idx += blockDim.x) {
+            const int tok = idx / width, j = idx - tok * width;
+            tm_copy_async(sv + tok * cols + j, v + (size_t)(first + t0 + tok) * stride + (size_t)head * dim + col0 + j);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    stage(0, 0);
+    int which = 0;
+    for (int t0 = 0; t0 < n; t0 += chunk, which ^= 1) {
+        const bool more = t0 + chunk < n;
+        if (more) {
+            stage(which ^ 1, t0 + chunk);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        const float* sr = tm_stage + which * set;
+        const float* sk = sr + chunk * padded;
+        const float* sw = sk + chunk * padded;
+        const float* sv = sw + chunk * padded;
+        const int m = min(chunk, n - t0);
         for (int tok = 0; tok < m; ++tok) {
             const float vj = active ? sv[tok * cols + c] : 0.0f;
-            const float* rr = sr + (size_t)tok * dim;
-            const float* kk = sk + (size_t)tok * dim;
-            const float* ww = sw + (size_t)tok * dim;
+            const float4* rr = (const float4*)(sr + tok * padded + part * TM_REGS);
+            const float4* kk = (const float4*)(sk + tok * padded + part * TM_REGS);
+            const float4* ww = (const float4*)(sw + tok * padded + part * TM_REGS);
             float acc = 0.0f;
 #pragma unroll
-            for (int j = 0; j < TM_REGS; ++j) {
-                const int i = j * key_split + part;
-                if (i < dim) {
-                    const float kv = kk[i] * vj;
-                    acc = fmaf(rr[i], fmaf(u[j], kv, S[j]), acc);
-                    S[j] = fmaf(ww[i], S[j], kv);
-                }
+            for (int q = 0; q < TM_REGS / 4; ++q) {
+                const float4 r4 = rr[q], k4 = kk[q], w4 = ww[q];
+                float kv;
+                kv = k4.x * vj; acc = fmaf(r4.x, fmaf(u[4 * q], kv, S[4 * q]), acc); S[4 * q] = fmaf(w4.x, S[4 * q], kv);
+                kv = k4.y * vj; acc = fmaf(r4.y, fmaf(u[4 * q + 1], kv, S[4 * q + 1]), acc); S[4 * q + 1] = fmaf(w4.y, S[4 * q + 1], kv);
+                kv = k4.z * vj; acc = fmaf(r4.z, fmaf(u[4 * q + 2], kv, S[4 * q + 2]), acc); S[4 * q + 2] = fmaf(w4.z, S[4 * q + 2], kv);
+                kv = k4.w * vj; acc = fmaf(r4.w, fmaf(u[4 * q + 3], kv, S[4 * q + 3]), acc); S[4 * q + 3] = fmaf(w4.w, S[4 * q + 3], kv);
             }
             for (int offset = key_split >> 1; offset > 0; offset >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, offset);
             if (part == 0 && active) out[(size_t)(first + t0 + tok) * stride + (size_t)head * dim + col] = acc;
         }
+        __syncthreads();                            // before the next round's copies land in this set
     }
 #pragma unroll
     for (int j = 0; j < TM_REGS; ++j) {
-        const int i = j * key_split + part;
+        const int i = part * TM_REGS + j;
         if (active && i < dim) s_write[(size_t)i * dim + col] = S[j];
     }
     if (head == 0 && blockIdx.z == 0) {
@@ -211,14 +255,17 @@ SKV_EXPORT int skv_token_shift_mix(const void* h, const float* mu, void* mixes, 
                       time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset));
 }
 
-// lora float [n, lora_stride] (the first `rank` columns count), w2 [channels, rank] in the compute dtype.
+// lora float [n, lora_stride] (the first `rank` columns count), w2t [rank, channels] (the weight transposed) in the
+// compute dtype.
 SKV_EXPORT int skv_time_mix_decay(const float* lora, int lora_stride, int rank, const void* w2, const float* w0,
                                   float* decay, int n, int channels, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (rank <= 0 || rank > 8192 || channels <= 0 || lora_stride < rank) return fail("skv_time_mix_decay", "sizes do not agree");
     if (!lora || !w2 || !w0 || !decay) return fail("skv_time_mix_decay", "a pointer is missing");
-    return launch_pdl("skv_time_mix_decay", time_mix_decay_kernel<skv_t>, dim3(n), dim3(256), (size_t)rank * sizeof(float),
-                      stream, lora, lora_stride, rank, (const skv_t*)w2, w0, decay, channels);
+    if ((size_t)TM_DECAY_TOKENS * rank * sizeof(float) > 48 * 1024) return fail("skv_time_mix_decay", "the rank is too large");
+    return launch_pdl("skv_time_mix_decay", time_mix_decay_kernel<skv_t>, dim3((n + TM_DECAY_TOKENS - 1) / TM_DECAY_TOKENS),
+                      dim3(256), (size_t)TM_DECAY_TOKENS * rank * sizeof(float), stream, lora, lora_stride, rank,
+                      (const skv_t*)w2, w0, decay, n, channels);
 }
 
 // r, k, v, decay, out: float [n, stride] with head `a` at columns a * dim; bonus float [heads, dim]; h [n, hidden] in the
@@ -233,11 +280,12 @@ SKV_EXPORT int skv_time_mix_scan(const float* r, const float* k, const float* v,
     if (!r || !k || !v || !decay || !bonus || !out || !h || !state) return fail("skv_time_mix_scan", "a pointer is missing");
     int key_split = 1;
     while (key_split * TM_REGS < dim) key_split *= 2;
-    const int cols = min(dim, 256 / key_split);
+    const int cols = min((dim + 3) & ~3, 256 / key_split);      // (a multiple of 4: the staged rows stay 16-byte aligned)
     const int slices = (dim + cols - 1) / cols;
-    int chunk = (int)(40 * 1024 / ((3 * (size_t)dim + cols) * sizeof(float)));
+    const int padded = key_split * TM_REGS;
+    int chunk = (int)(20 * 1024 / ((3 * (size_t)padded + cols) * sizeof(float)));       // two sets within 40 KB
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
-    const size_t smem = (size_t)chunk * (3 * (size_t)dim + cols) * sizeof(float);
+    const size_t smem = 2 * (size_t)chunk * (3 * (size_t)padded + cols) * sizeof(float);
     const int threads = ((cols * key_split + 31) / 32) * 32;
     return launch_pdl("skv_time_mix_scan", time_mix_scan_kernel<skv_t>, dim3(n_seqs, heads, slices), dim3(threads), smem,
                       stream, r, k, v, decay, stride, bonus, out, (const skv_t*)h, hidden, heads, dim, key_split, cols,

@@ -1070,11 +1070,12 @@ class Kernels:
             *self._state_args(step_meta, state, state_offset), _stream()), "token_shift_mix")
 
     def time_mix_decay(self, lora, rank: int, w2, w0, decay):
-        """``decay[t, c] = exp(-exp(w0[c] + w2[c] . tanh(lora[t, :rank])))`` (float32; ``w2`` in the compute dtype)."""
+        """``decay[t, c] = exp(-exp(w0[c] + w2[:, c] . tanh(lora[t, :rank])))`` (float32; ``w2`` ``[rank, channels]``, the
+        weight transposed, in the compute dtype)."""
         self._want(lora, torch.float32, "lora"); self._want(w2, self.dtype, "w2"); self._want(w0, torch.float32, "w0")
         self._want(decay, torch.float32, "decay")
         n, channels = decay.shape
-        if lora.shape[0] != n or lora.shape[1] < rank or tuple(w2.shape) != (channels, rank) or w0.numel() != channels:
+        if lora.shape[0] != n or lora.shape[1] < rank or tuple(w2.shape) != (rank, channels) or w0.numel() != channels:
             raise KernelError("time_mix_decay: shapes do not agree")
         self._check(self.lib.skv_time_mix_decay(_ptr(lora), lora.shape[1], int(rank), _ptr(w2), _ptr(w0), _ptr(decay), n,
                                                 channels, _stream()), "time_mix_decay")

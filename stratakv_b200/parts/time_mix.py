@@ -76,7 +76,7 @@ class TimeMix(Mixer):
         if self.rank_padded != s.decay_rank:          # (zero rows: the decay kernel reads the first decay_rank columns)
             w1 = torch.cat([w1, w1.new_zeros(self.rank_padded - s.decay_rank, s.hidden_size)], dim=0)
         self.w_1 = w1.contiguous()
-        self.w_2 = rt.upload(tensors[s.w2_weight]).contiguous()
+        self.w_2 = rt.upload(tensors[s.w2_weight]).t().contiguous()      # [rank, inner]: the decay kernel reads it by rows
         self.w0, self.bonus, self.norm = as_float(s.w0), as_float(s.bonus), as_float(s.norm)
         w_o = rt.upload(tensors[s.o_weight])
         if self.out_width != self.inner:

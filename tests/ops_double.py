@@ -485,7 +485,7 @@ class DoubleKernels:
 
     def time_mix_decay(self, lora, rank, w2, w0, decay):
         self.calls.append("time_mix_decay")
-        decay.copy_(torch.exp(-torch.exp(torch.tanh(lora[:, :rank]) @ w2.float().T + w0)))
+        decay.copy_(torch.exp(-torch.exp(torch.tanh(lora[:, :rank]) @ w2.float() + w0)))       # (w2 is [rank, channels])
 
     def time_mix_scan(self, r, k, v, decay, bonus, out, h, n_seqs, heads, dim, step_meta, state, state_offset=0):
         self.calls.append("time_mix_scan")

@@ -273,7 +273,7 @@ def test_time_mixing_over_portions_batches_and_used_slots(dtype, shape):
             for index, s in enumerate("rkvg"):                  # the library's projection is tested elsewhere
                 rows[index] = (mixes[index].double() @ mats[s].double().cuda().T).float()
             lora = (mixes[4].double() @ w1.double().cuda().T).float().contiguous()
-            ops.time_mix_decay(lora, rank, w2.cuda(), w0.cuda(), rows[4])
+            ops.time_mix_decay(lora, rank, w2.t().contiguous().cuda(), w0.cuda(), rows[4])
             ops.time_mix_scan(rows[0], rows[1], rows[2], rows[4], bonus.reshape(-1).cuda(), rows[5], h, len(live), heads,
                               dim, meta, state, 2)
             ops.time_mix_finish(rows[5], rows[3], norm_w.cuda(), eps, out_scale, out, heads, dim)
