@@ -32,7 +32,7 @@ struct TimeMixBatch {
 };
 
 constexpr int TM_MAX_MIXES = 8;
-constexpr int TM_REGS = 16;            // key channels of one value column that a thread of the scan keeps
+constexpr int TM_REGS = 16;            // key channels of one value column that a thread of the scan keeps (or 4)
 
 // mixes[s][t][c] = h[t][c] + (before[t][c] - h[t][c]) * mu[s][c]; a block per token, threads over the channels.
 template <typename T>
@@ -93,11 +93,35 @@ __device__ __forceinline__ void tm_copy_async(float* dst, const float* src) {
 }
 
 // The recurrence.  A block per (sequence, head, slice of value columns); thread (column c, part s of `key_split`) keeps
-// S[i][c] for the TM_REGS key channels i = s * TM_REGS ..; the tokens' r, k, w (the whole head, padded with zeros to
-// key_split * TM_REGS channels) and v (the block's columns) are staged in shared memory a few tokens at a time, the next
-// tokens' copies on their way while these are worked on.  The head-0 block of a sequence's first slice also remembers
-// the mixer's input at the sequence's last token.
-template <typename T>
+// S[i][c] for the TM_REGS key channels i = s * TM_REGS ..; the tokens' r, k, w (the whole head) and v (the block's
+// columns) are staged in shared memory a few tokens at a time, the next tokens' copies on their way while these are
+// worked on.  A part's TM_REGS channels lie TM_PART_STRIDE floats from the next part's, so that the four parts a quarter
+// of a warp reads at once fall into different banks; channels past the head's last stay zero.  A thread fetches the
+// next token's numbers from shared memory before it works on this token's.  The head-0 block of a sequence's first
+// slice also remembers the mixer's input at the sequence's last token.
+// REGS is 16 where a step has blocks enough to fill the GPU, and 4 where it has not (one prompt alone): a thread then
+// has a quarter of the sums to make one after the other and a warp's shuffles bring four times as many together.
+template <int REGS> struct TimeMixLayout { static constexpr int stride = REGS == 16 ? 20 : REGS; };
+
+template <int REGS>
+struct TimeMixToken {
+    float4 r[REGS / 4], k[REGS / 4], w[REGS / 4];
+    float v;
+};
+
+template <int REGS>
+__device__ __forceinline__ void tm_fetch(TimeMixToken<REGS>& token, const float* sr, const float* sk, const float* sw,
+                                         const float* sv, int row, int column, bool active) {
+#pragma unroll
+    for (int q = 0; q < REGS / 4; ++q) {
+        token.r[q] = ((const float4*)(sr + row))[q];
+        token.k[q] = ((const float4*)(sk + row))[q];
+        token.w[q] = ((const float4*)(sw + row))[q];
+    }
+    token.v = active ? sv[column] : 0.0f;
+}
+
+template <typename T, int REGS>
 __global__ void __launch_bounds__(256)
 time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
                      const float* __restrict__ decay, int stride, const float* __restrict__ bonus,
@@ -116,11 +140,11 @@ time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, c
     float* s_write = slot_state + (size_t)((p0 + n - 1) & 1) * half + (size_t)head * dim * dim;
     const int part = threadIdx.x % key_split, c = threadIdx.x / key_split, col = col0 + c;
     const bool active = c < cols && col < dim;
-    const int padded = key_split * TM_REGS;
-    float S[TM_REGS], u[TM_REGS];
+    const int padded = key_split * TimeMixLayout<REGS>::stride;
+    float S[REGS], u[REGS];
 #pragma unroll
-    for (int j = 0; j < TM_REGS; ++j) {
-        const int i = part * TM_REGS + j;
+    for (int j = 0; j < REGS; ++j) {
+        const int i = part * REGS + j;
         const bool held = active && i < dim;
         S[j] = held && p0 > 0 ? s_read[(size_t)i * dim + col] : 0.0f;
         u[j] = held ? bonus[(size_t)head * dim + i] : 0.0f;
@@ -139,9 +163,10 @@ time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, c
         for (int idx = threadIdx.x; idx < m * dim; idx += blockDim.x) {
             const int tok = idx / dim, i = idx - tok * dim;
             const size_t at = (size_t)(first + t0 + tok) * stride + (size_t)head * dim + i;
-            tm_copy_async(sr + tok * padded + i, r + at);
-            tm_copy_async(sk + tok * padded + i, k + at);
-            tm_copy_async(sw + tok * padded + i, decay + at);
+            const int to = tok * padded + (i / REGS) * TimeMixLayout<REGS>::stride + (i % REGS);
+            tm_copy_async(sr + to, r + at);
+            tm_copy_async(sk + to, k + at);
+            tm_copy_async(sw + to, decay + at);
         }
         const int width = min(cols, dim - col0);
         for (int idx = threadIdx.x; idx < m * width; idx += blockDim.x) {
@@ -167,15 +192,15 @@ time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, c
         const float* sw = sk + chunk * padded;
         const float* sv = sw + chunk * padded;
         const int m = min(chunk, n - t0);
-        for (int tok = 0; tok < m; ++tok) {
-            const float vj = active ? sv[tok * cols + c] : 0.0f;
-            const float4* rr = (const float4*)(sr + tok * padded + part * TM_REGS);
-            const float4* kk = (const float4*)(sk + tok * padded + part * TM_REGS);
-            const float4* ww = (const float4*)(sw + tok * padded + part * TM_REGS);
+        const int mine = part * TimeMixLayout<REGS>::stride;
+        float* to = out + (size_t)(first + t0) * stride + (size_t)head * dim + col;
+        // one token: its share of o (summed over the parts by shuffles) and the new S
+        auto work = [&](const TimeMixToken<REGS>& now) {
+            const float vj = now.v;
             float acc = 0.0f;
 #pragma unroll
-            for (int q = 0; q < TM_REGS / 4; ++q) {
-                const float4 r4 = rr[q], k4 = kk[q], w4 = ww[q];
+            for (int q = 0; q < REGS / 4; ++q) {
+                const float4 r4 = now.r[q], k4 = now.k[q], w4 = now.w[q];
                 float kv;
                 kv = k4.x * vj; acc = fmaf(r4.x, fmaf(u[4 * q], kv, S[4 * q]), acc); S[4 * q] = fmaf(w4.x, S[4 * q], kv);
                 kv = k4.y * vj; acc = fmaf(r4.y, fmaf(u[4 * q + 1], kv, S[4 * q + 1]), acc); S[4 * q + 1] = fmaf(w4.y, S[4 * q + 1], kv);
@@ -183,13 +208,25 @@ time_mix_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, c
                 kv = k4.w * vj; acc = fmaf(r4.w, fmaf(u[4 * q + 3], kv, S[4 * q + 3]), acc); S[4 * q + 3] = fmaf(w4.w, S[4 * q + 3], kv);
             }
             for (int offset = key_split >> 1; offset > 0; offset >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, offset);
-            if (part == 0 && active) out[(size_t)(first + t0 + tok) * stride + (size_t)head * dim + col] = acc;
+            if (part == 0 && active) *to = acc;
+            to += stride;
+        };
+        // two tokens a round, each fetched from shared memory while the other is worked on
+        TimeMixToken<REGS> even, odd;
+        tm_fetch(even, sr, sk, sw, sv, mine, c, active);
+        for (int tok = 0; tok < m; tok += 2) {
+            if (tok + 1 < m) tm_fetch(odd, sr, sk, sw, sv, (tok + 1) * padded + mine, (tok + 1) * cols + c, active);
+            work(even);
+            if (tok + 1 < m) {
+                if (tok + 2 < m) tm_fetch(even, sr, sk, sw, sv, (tok + 2) * padded + mine, (tok + 2) * cols + c, active);
+                work(odd);
+            }
         }
         __syncthreads();                            // before the next round's copies land in this set
     }
 #pragma unroll
-    for (int j = 0; j < TM_REGS; ++j) {
-        const int i = part * TM_REGS + j;
+    for (int j = 0; j < REGS; ++j) {
+        const int i = part * REGS + j;
         if (active && i < dim) s_write[(size_t)i * dim + col] = S[j];
     }
     if (head == 0 && blockIdx.z == 0) {
@@ -278,18 +315,34 @@ SKV_EXPORT int skv_time_mix_scan(const float* r, const float* k, const float* v,
     if (heads <= 0 || dim <= 0 || dim > 32 * TM_REGS || heads > 65535)
         return fail("skv_time_mix_scan", "heads of 1 to 512 numbers are served");
     if (!r || !k || !v || !decay || !bonus || !out || !h || !state) return fail("skv_time_mix_scan", "a pointer is missing");
+    // Few blocks (one prompt alone): four key channels a thread, so that a head's work spreads over four times the
+    // threads; else sixteen.
+    const long long blocks = (long long)n_seqs * heads;
+    const int regs = blocks * 4 <= sm_count() * 2 && dim <= 128 ? 4 : TM_REGS;
     int key_split = 1;
-    while (key_split * TM_REGS < dim) key_split *= 2;
-    const int cols = min((dim + 3) & ~3, 256 / key_split);      // (a multiple of 4: the staged rows stay 16-byte aligned)
+    while (key_split * regs < dim) key_split *= 2;
+    // The value columns of a head are cut into slices (blocks) so that a step of few sequences still fills the GPU: a
+    // slice of at least 8 columns, a multiple of 4 (the staged rows stay 16-byte aligned), at most 256 threads.
+    int cols = min((dim + 3) & ~3, 256 / key_split);
+    if (blocks < sm_count()) {
+        const int wanted = (int)((sm_count() + blocks - 1) / blocks);
+        const int fewer = (((dim + wanted - 1) / wanted) + 3) & ~3;
+        cols = max(8, min(cols, fewer));
+    }
     const int slices = (dim + cols - 1) / cols;
-    const int padded = key_split * TM_REGS;
+    const int padded = key_split * (regs == 16 ? TimeMixLayout<16>::stride : TimeMixLayout<4>::stride);
     int chunk = (int)(20 * 1024 / ((3 * (size_t)padded + cols) * sizeof(float)));       // two sets within 40 KB
     chunk = chunk < 1 ? 1 : (chunk > 16 ? 16 : chunk);
     const size_t smem = 2 * (size_t)chunk * (3 * (size_t)padded + cols) * sizeof(float);
     const int threads = ((cols * key_split + 31) / 32) * 32;
-    return launch_pdl("skv_time_mix_scan", time_mix_scan_kernel<skv_t>, dim3(n_seqs, heads, slices), dim3(threads), smem,
+    const TimeMixBatch batch = time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset);
+    if (regs == 4)
+        return launch_pdl("skv_time_mix_scan", time_mix_scan_kernel<skv_t, 4>, dim3(n_seqs, heads, slices), dim3(threads), smem,
+                          stream, r, k, v, decay, stride, bonus, out, (const skv_t*)h, hidden, heads, dim, key_split, cols,
+                          chunk, batch);
+    return launch_pdl("skv_time_mix_scan", time_mix_scan_kernel<skv_t, 16>, dim3(n_seqs, heads, slices), dim3(threads), smem,
                       stream, r, k, v, decay, stride, bonus, out, (const skv_t*)h, hidden, heads, dim, key_split, cols,
-                      chunk, time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset));
+                      chunk, batch);
 }
 
 // o and gate float [n, stride]; norm float [heads * dim]; out [n, out_stride] in the compute dtype.
