@@ -225,6 +225,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         }
         const int head = head0 + r;
         if (splits == 1) {
+            // a sink counts once in the denominator (scores here are in units of log2)
+            if (extras.sink) sum += dec_exp2(extras.sink[head] * 1.4426950408889634f - m);
             out[((size_t)seq * num_heads + head) * DHD + d] =
                 __float2bfloat16_rn(total / sum * gate_factor(extras, seq, head) * gate_element(extras, seq, head, DHD, d));
         } else {
@@ -255,6 +257,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ partial_o, const
             total += weight * partial_o[at * DHD + d];
             sum += weight * partial_ml[2 * at + 1];
         }
+        if (extras.sink) sum += dec_exp2(extras.sink[item % num_heads] * 1.4426950408889634f - m);
         out[item * DHD + d] = __float2bfloat16_rn(total / sum * gated *
                                                   gate_element(extras, item / num_heads, (int)(item % num_heads), DHD, d));
     }
@@ -266,18 +269,20 @@ using namespace skv;
 
 // Scratch the caller provides when splits > 1: partial_o [n_seqs * heads * splits * head_dim] floats,
 // partial_ml [n_seqs * heads * splits * 2] floats.
-// `bias` [num_heads][bias_len] and `gate` (logits, rows gate_stride apart) may be null: see AttentionExtras.
-SKV_EXPORT int skv_attention_decode_extras(const void* q, const void* k_cache, const void* v_cache,
-                                           const int* block_table, int table_width, const int* ctx_after, void* out,
-                                           float* partial_o, float* partial_ml, int n_seqs, int num_heads,
-                                           int num_kv_heads, int head_dim, int block_size, float scale, int window,
-                                           int splits, const float* bias, int bias_len, const float* gate,
-                                           int gate_stride, float softcap, int gate_per_element, cudaStream_t stream) {
+// `bias` [num_heads][bias_len], `gate` (logits, rows gate_stride apart) and `sink` [num_heads] may be null: see
+// AttentionExtras.
+SKV_EXPORT int skv_attention_decode_sink(const void* q, const void* k_cache, const void* v_cache,
+                                         const int* block_table, int table_width, const int* ctx_after, void* out,
+                                         float* partial_o, float* partial_ml, int n_seqs, int num_heads,
+                                         int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                         int splits, const float* bias, int bias_len, const float* gate,
+                                         int gate_stride, float softcap, int gate_per_element, const float* sink,
+                                         cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if ((bias && bias_len <= 0) || (gate && gate_stride < num_heads * (gate_per_element ? head_dim : 1)) ||
         (gate_per_element && !gate) || softcap < 0.0f)
         return fail("skv_attention_decode", "a bias table needs its length, a gate rows of at least heads numbers (heads * head_dim with a gate per number), a cap must not be negative");
-    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element};
+    const AttentionExtras extras = {bias, bias_len, gate, gate_stride, softcap, gate_per_element, sink};
     if (head_dim != DHD) return fail("skv_attention_decode", "this library was built for another head size");
     if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads != 0)
         return fail("skv_attention_decode", "heads must be a positive multiple of kv heads");
@@ -310,6 +315,17 @@ SKV_EXPORT int skv_attention_decode_extras(const void* q, const void* k_cache, c
                           dim3(DHD >= 128 ? 128 : 64), 0, stream, (const float*)partial_o,
                           (const float*)partial_ml, (__nv_bfloat16*)out, splits, num_heads, extras);
     return 0;
+}
+
+SKV_EXPORT int skv_attention_decode_extras(const void* q, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int table_width, const int* ctx_after, void* out,
+                                           float* partial_o, float* partial_ml, int n_seqs, int num_heads,
+                                           int num_kv_heads, int head_dim, int block_size, float scale, int window,
+                                           int splits, const float* bias, int bias_len, const float* gate,
+                                           int gate_stride, float softcap, int gate_per_element, cudaStream_t stream) {
+    return skv_attention_decode_sink(q, k_cache, v_cache, block_table, table_width, ctx_after, out, partial_o, partial_ml,
+                                     n_seqs, num_heads, num_kv_heads, head_dim, block_size, scale, window, splits, bias,
+                                     bias_len, gate, gate_stride, softcap, gate_per_element, nullptr, stream);
 }
 
 SKV_EXPORT int skv_attention_decode(const void* q, const void* k_cache, const void* v_cache,
@@ -421,6 +437,12 @@ SKV_EXPORT int skv_attention_decode(const void*, const void*, const void*, const
 SKV_EXPORT int skv_attention_decode_extras(const void*, const void*, const void*, const int*, int, const int*, void*,
                                            float*, float*, int, int, int, int, int, float, int, int, const float*, int,
                                            const float*, int, float, int, cudaStream_t) {
+    return skv::fail("skv_attention_decode", "the float32 build has no split decode kernel: use skv_attention");
+}
+
+SKV_EXPORT int skv_attention_decode_sink(const void*, const void*, const void*, const int*, int, const int*, void*,
+                                         float*, float*, int, int, int, int, int, float, int, int, const float*, int,
+                                         const float*, int, float, int, const float*, cudaStream_t) {
     return skv::fail("skv_attention_decode", "the float32 build has no split decode kernel: use skv_attention");
 }
 

@@ -55,8 +55,8 @@ token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ mu, T*
     }
 }
 
-// decay[t][c] = exp(-exp(w0[c] + sum_j w2t[j][c] * tanh(lora[t][j]))); a block per TM_DECAY_TOKENS tokens, threads over
-// the channels (w2t is the weight transposed, [rank][channels], so that neighbouring threads read neighbouring numbers
+// decay[t][c] = exp(-exp(w0[c] + sum_j w2t[j][c] * tanh(lora[t][j]))); a block per TM_DECAY_TOKENS tokens and 256
+// channels, a thread a channel (w2t is the weight transposed, [rank][channels], so that neighbouring threads read neighbouring numbers
 // and a number that is read serves all of the block's tokens).
 constexpr int TM_DECAY_TOKENS = 4;
 template <typename T>
@@ -73,7 +73,8 @@ time_mix_decay_kernel(const float* __restrict__ lora, int lora_stride, int rank,
         tm_lora[idx] = tok < count ? tanhf(lora[(size_t)(t0 + tok) * lora_stride + j]) : 0.0f;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c < channels) {
         float z[TM_DECAY_TOKENS];
 #pragma unroll
         for (int tok = 0; tok < TM_DECAY_TOKENS; ++tok) z[tok] = w0[c];
@@ -300,8 +301,8 @@ SKV_EXPORT int skv_time_mix_decay(const float* lora, int lora_stride, int rank, 
     if (rank <= 0 || rank > 8192 || channels <= 0 || lora_stride < rank) return fail("skv_time_mix_decay", "sizes do not agree");
     if (!lora || !w2 || !w0 || !decay) return fail("skv_time_mix_decay", "a pointer is missing");
     if ((size_t)TM_DECAY_TOKENS * rank * sizeof(float) > 48 * 1024) return fail("skv_time_mix_decay", "the rank is too large");
-    return launch_pdl("skv_time_mix_decay", time_mix_decay_kernel<skv_t>, dim3((n + TM_DECAY_TOKENS - 1) / TM_DECAY_TOKENS),
-                      dim3(256), (size_t)TM_DECAY_TOKENS * rank * sizeof(float), stream, lora, lora_stride, rank,
+    return launch_pdl("skv_time_mix_decay", time_mix_decay_kernel<skv_t>,
+                      dim3((n + TM_DECAY_TOKENS - 1) / TM_DECAY_TOKENS, (channels + 255) / 256), dim3(256), (size_t)TM_DECAY_TOKENS * rank * sizeof(float), stream, lora, lora_stride, rank,
                       (const skv_t*)w2, w0, decay, n, channels);
 }
 

@@ -113,7 +113,9 @@ def fidolix_spec(config: FidolixConfig) -> ModelSpec:
         architecture=config.architecture, hidden_size=config.width, vocab_size=config.vocab,
         embedding=EmbeddingSpec(config.vocab, config.width, "embed", scale=config.embedding_scale),
         layers=tuple(layers), schedule=schedule, final_norm=NormSpec(config.width, config.norm_eps, "final.norm"),
-        head=HeadSpec(config.vocab, config.width, "head"))
+        head=HeadSpec(config.vocab, config.width, "head"),
+        # a layer without a feed-forward has no use for a second norm; a checkpoint may carry one all the same
+        ignorable=tuple(f"l{i}.norm2" for i, layer in enumerate(config.layers) if layer.mlp is None))
 
 
 register_architecture(ARCHITECTURE, FidolixConfig, fidolix_spec)

@@ -373,8 +373,8 @@ class Kernels:
     def attention_decode(self, q, k_cache, v_cache, block_table, ctx_after, out, num_heads: int,
                          num_kv_heads: int, head_dim: int, block_size: int, scale: float, window: int = 0,
                          splits: int = 1, scratch_o=None, scratch_ml=None, bias=None, gate=None, gate_stride: int = 0,
-                         softcap: float = 0.0, gate_per_element: bool = False):
-        """(``bias``, ``gate``: as in ``attention_prefill``; ``softcap``, ``gate_per_element``: as in
+                         softcap: float = 0.0, gate_per_element: bool = False, sink=None):
+        """(``bias``, ``gate``: as in ``attention_prefill``; ``softcap``, ``gate_per_element``, ``sink``: as in
         ``attention_prefill_tc``.)
         One new token per sequence (bfloat16 build): ``ctx_after[s]`` keys are cached for sequence
         ``s``, the newest being the query's own.  ``splits`` > 1 cuts each context across blocks and
@@ -389,12 +389,16 @@ class Kernels:
             self._want(scratch_o, torch.float32, "scratch_o"); self._want(scratch_ml, torch.float32, "scratch_ml")
             if scratch_o.numel() < n * num_heads * splits * head_dim or scratch_ml.numel() < n * num_heads * splits * 2:
                 raise KernelError("attention_decode: scratch is too small for this many splits")
-        self._check(self.lib.skv_attention_decode_extras(
+        if sink is not None:
+            self._want(sink, torch.float32, "sink")
+            if sink.numel() != num_heads:
+                raise KernelError("attention_decode: the sink must hold one number per head")
+        self._check(self.lib.skv_attention_decode_sink(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(ctx_after),
             _ptr(out), _ptr(scratch_o), _ptr(scratch_ml), n, num_heads, num_kv_heads, head_dim, block_size,
             ctypes.c_float(scale), window, splits,
             *self._extras(bias, gate, gate_stride, num_heads, "attention_decode", head_dim if gate_per_element else 0),
-            ctypes.c_float(softcap), int(bool(gate_per_element)), _stream()), "attention_decode")
+            ctypes.c_float(softcap), int(bool(gate_per_element)), _ptr(sink), _stream()), "attention_decode")
 
     def has_attention_decode_fused(self) -> bool:
         return bool(self.lib.skv_has_attention_decode_fused())

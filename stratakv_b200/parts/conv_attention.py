@@ -12,8 +12,8 @@ For the mixer's input h, H query heads on G key heads of d numbers::
 Kernels: one projection ``[q | k]`` (float32 out), ``short_conv_rotary`` (bias, convolution, rotation, queries out, keys
 and values into the paged cache; all float32), ``short_conv_remember`` (the state a sequence keeps: the biased
 projections of its last ``taps - 1`` positions), attention over the cache (prompts of head size 64 or 128 in bfloat16 on
-the tensor-core kernel, everything else on the kernel with run-time head sizes, one-token steps with the keys cut into
-parts), the output projection.  ``state_offset`` (floats): where this mixer's state starts in its cache entry's rows, for
+the tensor-core kernel and their one-token steps on the split kernel, everything else on the kernel with run-time head
+sizes, its one-token steps with the keys cut into parts), the output projection.  ``state_offset`` (floats): where this mixer's state starts in its cache entry's rows, for
 a mixer that shares the entry with another.
 """
 from __future__ import annotations
@@ -137,6 +137,22 @@ class ConvAttention(Mixer):
             rt.kernels(s.head_dim).attention_prefill_tc(
                 q, k_cache, v_cache, table, step.cu_q, step.ctx_after, ctx, step.max_q_len, s.num_heads, s.num_kv_heads,
                 s.head_dim, block_size, s.scale, s.window, sink=self.sink)
+            return
+        if (step.is_decode and rt.dtype == torch.bfloat16 and rt.device.type == "cuda" and s.head_dim in (64, 128)
+                and self.ctx_width == self.q_dim and block_size % 16 == 0):
+            # one token a sequence at a head size the split kernel is built for: the query heads of a key head as
+            # rows of a tensor-core product, the context in pieces, the sink in the merge
+            from .attention import decode_splits
+            blocks_per_seq = s.num_kv_heads * (-(-(s.num_heads // s.num_kv_heads) // 16))
+            keys = min(step.max_ctx, s.window) if s.window > 0 else step.max_ctx
+            splits = decode_splits(n, blocks_per_seq, keys, rt.sm_count)
+            scratch_o = scratch_ml = None
+            if splits > 1:
+                scratch_o = rt.workspace.get("attn_split_o", (n * s.num_heads * splits * s.head_dim,), torch.float32)
+                scratch_ml = rt.workspace.get("attn_split_ml", (n * s.num_heads * splits * 2,), torch.float32)
+            rt.kernels(s.head_dim).attention_decode(q, k_cache, v_cache, table, step.ctx_after, ctx, s.num_heads,
+                                                    s.num_kv_heads, s.head_dim, block_size, s.scale, s.window, splits,
+                                                    scratch_o, scratch_ml, sink=self.sink)
             return
         splits, scratch_o, scratch_ml = 1, None, None
         if step.is_decode:

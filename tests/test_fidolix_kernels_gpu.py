@@ -218,6 +218,16 @@ def test_a_key_that_dominates_at_the_edges_of_the_window(dtype, shape):
         if p < T:
             for splits in (1, 2, 5):
                 close(general(p, 1, splits), want[p:p + 1], dtype, f"position {p} alone, keys in {splits} parts")
+    if dtype == torch.bfloat16 and dim in (64, 128):
+        # one token a sequence on the split kernel of the head size's own library, the sink in its merge
+        for p in sorted({0, 1, block_size - 1, block_size, 200, 200 + reach - 1, min(T - 1, 200 + reach), T - 1}):
+            for splits in (1, 2, 5):
+                out = torch.empty(1, heads * dim, dtype=dtype, device="cuda")
+                scratch_o = torch.empty(heads * splits * dim, device="cuda") if splits > 1 else None
+                scratch_ml = torch.empty(heads * splits * 2, device="cuda") if splits > 1 else None
+                ops.attention_decode(q_rows[p:p + 1].contiguous(), k_cache, v_cache, table, i32([p + 1]), out, heads,
+                                     kv_heads, dim, block_size, scale, window, splits, scratch_o, scratch_ml, sink=sink_f)
+                close(out, want[p:p + 1], dtype, f"the split kernel at position {p}, {splits} pieces", loose=2.0)
     if dtype == torch.bfloat16 and dim in (64, 128) and ops.has_attention_prefill_tc():
         for first in (0, 150):
             count = T - first
