@@ -33,7 +33,8 @@ class TokenEmbedding(Part):
     def forward(self, step, x, flags, stats=None) -> None:
         """Fill the stream ``x`` [tokens, hidden] for ``step.token_ids``; an id outside the table raises
         bit 0 of ``flags``.  ``stats``: see ``residual.ResidualStats`` (the kernel fills it where it can)."""
-        scale = getattr(self.spec, "scale", 1.0)
+        # (a class that builds on this one for another kind of spec scales, or does not, by itself)
+        scale = getattr(self.spec, "scale", 1.0) if getattr(self.spec, "kind", None) == "embedding" else 1.0
         # (a scaled row is not what the folded norm's statistics were taken of: the norm then runs as a kernel)
         self.rt.kernels().embed(self.table, step.token_ids, x, flags, stats=stats if scale == 1.0 else None)
         if scale != 1.0:
