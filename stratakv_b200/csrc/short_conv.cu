@@ -105,6 +105,44 @@ short_conv_rotary_kernel(const float* __restrict__ rows, int row_stride, const f
         if (v_cache) plain = v_cache + row * dim;
     }
     const int half = rotated >> 1;
+    if (interleaved && !(dim & 1) && !(row_stride & 1) && taps <= 8) {
+        // a lane owns the pair (2i, 2i + 1): both numbers of every tap in one load, no number computed twice
+        for (int pr = lane; pr < (dim >> 1); pr += 32) {
+            const int c = c0 + 2 * pr;
+            const float2 b = bias ? *(const float2*)(bias + c) : make_float2(0.0f, 0.0f);
+            float2 sum;
+            if (taps <= 1) {
+                const float2 u = *(const float2*)(rows + (size_t)t * row_stride + c);
+                sum = make_float2((u.x + b.x) * (taps == 1 ? conv_w[c] : 1.0f), (u.y + b.y) * (taps == 1 ? conv_w[c + 1] : 1.0f));
+            } else {
+                sum = make_float2(0.0f, 0.0f);
+                for (int j = 0; j < taps; ++j) {
+                    const int back = taps - 1 - j;
+                    if (p - back < 0) continue;
+                    float2 u;
+                    if (t - back >= first) {
+                        u = *(const float2*)(rows + (size_t)(t - back) * row_stride + c);
+                        u.x += b.x; u.y += b.y;
+                    } else {
+                        const float* kept = ring + (size_t)((p - back) % taps) * channels + c;
+                        u = make_float2(kept[0], kept[1]);
+                    }
+                    sum.x = fmaf(conv_w[(size_t)c * taps + j], u.x, sum.x);
+                    sum.y = fmaf(conv_w[(size_t)(c + 1) * taps + j], u.y, sum.y);
+                }
+            }
+            const int d = 2 * pr;
+            if (plain) { plain[d] = from_float<T>(sum.x); plain[d + 1] = from_float<T>(sum.y); }
+            float2 turned = sum;
+            if (d < rotated) {
+                const float2 cs = cos_sin[(size_t)p * half + pr];
+                turned = make_float2(sum.x * cs.x - sum.y * cs.y, sum.y * cs.x + sum.x * cs.y);
+            }
+            out[d] = from_float<T>(turned.x);
+            out[d + 1] = from_float<T>(turned.y);
+        }
+        return;
+    }
     for (int d = lane; d < dim; d += 32) {
         const float mine = convolved(rows, row_stride, bias, conv_w, ring, channels, taps, t, p, first, c0 + d);
         if (plain) plain[d] = from_float<T>(mine);

@@ -34,8 +34,35 @@ struct TimeMixBatch {
 constexpr int TM_MAX_MIXES = 8;
 constexpr int TM_REGS = 16;            // key channels of one value column that a thread of the scan keeps (or 4)
 
-// mixes[s][t][c] = h[t][c] + (before[t][c] - h[t][c]) * mu[s][c]; a block per token, threads over the channels.
-template <typename T>
+// Eight neighbouring numbers of a row, as floats (16 bytes of bfloat16 or 32 of float at a time).
+__device__ __forceinline__ void tm_load8(const float* p, float* v) {
+    const float4 a = ((const float4*)p)[0], b = ((const float4*)p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void tm_load8(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *(const uint4*)p;
+    const __nv_bfloat162* pairs = (const __nv_bfloat162*)&raw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(pairs[i]);
+        v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void tm_store8(float* p, const float* v) {
+    ((float4*)p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    ((float4*)p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void tm_store8(__nv_bfloat16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* pairs = (__nv_bfloat162*)&raw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pairs[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *(uint4*)p = raw;
+}
+
+// mixes[s][t][c] = h[t][c] + (before[t][c] - h[t][c]) * mu[s][c]; a block per token, threads over the channels (VEC: eight
+// channels a thread where the width is a multiple of 8 and the rows are 16-byte aligned).
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ mu, T* __restrict__ mixes, int n_tokens,
                        int hidden, int n_mixes, long long before_offset, const TimeMixBatch batch) {
@@ -46,6 +73,27 @@ token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ mu, T*
     const bool inside = t > batch.cu_q[s];
     const float* kept = batch.state + (size_t)batch.slot_ids[s] * batch.state_stride + batch.state_offset + before_offset +
                         (size_t)((p - 1) & 1) * hidden;
+    if (VEC) {
+        for (int c = 8 * threadIdx.x; c < hidden; c += 8 * blockDim.x) {
+            float now[8], before[8], factor[8], mixed[8];
+            tm_load8(h + (size_t)t * hidden + c, now);
+            if (inside) {
+                tm_load8(h + (size_t)(t - 1) * hidden + c, before);
+            } else if (p > 0) {
+                tm_load8(kept + c, before);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) before[i] = 0.0f;
+            }
+            for (int m = 0; m < n_mixes; ++m) {
+                tm_load8(mu + (size_t)m * hidden + c, factor);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mixed[i] = fmaf(before[i] - now[i], factor[i], now[i]);
+                tm_store8(mixes + ((size_t)m * n_tokens + t) * hidden + c, mixed);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float now = to_float(h[(size_t)t * hidden + c]);
         const float before = inside ? to_float(h[(size_t)(t - 1) * hidden + c]) : (p > 0 ? kept[c] : 0.0f);
@@ -288,9 +336,16 @@ SKV_EXPORT int skv_token_shift_mix(const void* h, const float* mu, void* mixes, 
     if (n <= 0) return 0;
     if (hidden <= 0 || n_mixes <= 0 || n_mixes > TM_MAX_MIXES) return fail("skv_token_shift_mix", "1 to 8 mixes are served");
     if (!h || !mu || !mixes || !state) return fail("skv_token_shift_mix", "rows, factors, state and a place for the mixes are needed");
-    return launch_pdl("skv_token_shift_mix", token_shift_mix_kernel<skv_t>, dim3(n), dim3(256), 0, stream,
-                      (const skv_t*)h, mu, (skv_t*)mixes, n, hidden, n_mixes, 2LL * heads * dim * dim,
-                      time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset));
+    const long long before_offset = 2LL * heads * dim * dim;
+    const TimeMixBatch batch = time_mix_batch(positions, token_seq, cu_q, slot_ids, state, state_stride, state_offset);
+    // eight channels a thread where every row that is read or written starts on 16 bytes (32 for floats)
+    const bool vec = hidden % 8 == 0 && !(((uintptr_t)h | (uintptr_t)mixes | (uintptr_t)mu | (uintptr_t)state) & 31) &&
+                     state_stride % 8 == 0 && (state_offset + before_offset) % 8 == 0;
+    if (vec)
+        return launch_pdl("skv_token_shift_mix", token_shift_mix_kernel<skv_t, true>, dim3(n), dim3(256), 0, stream,
+                          (const skv_t*)h, mu, (skv_t*)mixes, n, hidden, n_mixes, before_offset, batch);
+    return launch_pdl("skv_token_shift_mix", token_shift_mix_kernel<skv_t, false>, dim3(n), dim3(256), 0, stream,
+                      (const skv_t*)h, mu, (skv_t*)mixes, n, hidden, n_mixes, before_offset, batch);
 }
 
 // lora float [n, lora_stride] (the first `rank` columns count), w2t [rank, channels] (the weight transposed) in the
